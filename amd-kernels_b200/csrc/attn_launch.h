@@ -1,0 +1,28 @@
+// Host-side declarations shared by the C-ABI translation unit and the kernel
+// translation units.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "tail_plan.h"
+
+namespace ma {
+
+struct AttnParams;
+
+// One CTA per 128-row query tile, fully serialised (cross-check kernel).
+cudaError_t launch_attn_simple(const AttnParams& p, cudaStream_t stream);
+
+// Persistent warp-specialised kernel; `grid` CTAs walk the unit list of the plan.
+cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, cudaStream_t stream);
+
+// Combines the partial results of KV-split tasks into the bf16 output.
+cudaError_t launch_merge_parts(const AttnParams& p, cudaStream_t stream);
+
+// dst[i] = bf16(src[i]) with the given rounding mode (device pointers); exposes the
+// epilogue's rounding code for exhaustive bit-pattern tests.
+cudaError_t launch_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, cudaStream_t stream);
+
+}  // namespace ma

@@ -1,0 +1,197 @@
+// C ABI of the library (declared in include/moonmath_attention.h): argument
+// checks, tensor maps, tail plan, kernel launches.  Keeps no state between
+// calls apart from the lazily resolved driver entry point.
+#include <cmath>
+#include <cstring>
+
+#include "../../include/moonmath_attention.h"
+#include "attn_common.cuh"
+#include "attn_launch.h"
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      f = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(f);
+  }();
+  return fn;
+}
+
+// Rank-4 map over a contiguous bf16 tensor, rows of 128 head-dim elements.
+// The sequence axis is a dimension of its own, so a box that runs past the end
+// of a sequence reads zeros instead of the next head or batch.
+int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int seq, int bshd) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return MA_ERR_DRIVER;
+  const cuuint64_t row = ma::kHeadDim * 2;  // bytes
+  cuuint64_t dims[4], strides[3];
+  cuuint32_t box[4];
+  if (bshd) {  // [B, S, H, D]
+    dims[0] = ma::kHeadDim, dims[1] = heads, dims[2] = seq, dims[3] = batch;
+    strides[0] = row, strides[1] = row * heads, strides[2] = row * heads * seq;
+    box[0] = 64, box[1] = 1, box[2] = ma::kTileN, box[3] = 1;
+  } else {  // [B, H, S, D]
+    dims[0] = ma::kHeadDim, dims[1] = seq, dims[2] = heads, dims[3] = batch;
+    strides[0] = row, strides[1] = row * seq, strides[2] = row * seq * heads;
+    box[0] = 64, box[1] = ma::kTileN, box[2] = 1, box[3] = 1;
+  }
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MA_OK : MA_ERR_TENSOR_MAP;
+}
+
+int cuda_rc(cudaError_t e) { return e == cudaSuccess ? MA_OK : MA_ERR_CUDA_BASE + static_cast<int>(e); }
+
+int check_dims(int batch, int heads, int seq_len, int seq_len_kv) {
+  if (batch <= 0 || heads <= 0) return MA_ERR_BATCH_HEADS;
+  if (seq_len <= 0) return MA_ERR_SEQ_Q;
+  if (seq_len_kv <= 0) return MA_ERR_SEQ_KV;
+  // Unit indices and grid.y are 32-bit / 16-bit quantities.
+  const long long bh = static_cast<long long>(batch) * heads;
+  const long long tasks = bh * ((seq_len + ma::kPlanTaskRows - 1) / ma::kPlanTaskRows);
+  if (bh > 65535 || tasks > (1ll << 30)) return MA_ERR_TOO_LARGE;
+  return MA_OK;
+}
+
+int resolve_sms(int num_sms) {
+  if (num_sms > 0) return num_sms;
+  return ma_device_sms();
+}
+
+}  // namespace
+
+extern "C" {
+
+int ma_abi_version(void) { return MA_ABI_VERSION; }
+
+const char* ma_error_string(int rc) {
+  switch (rc) {
+    case MA_OK: return "ok";
+    case MA_ERR_BATCH_HEADS: return "batch and heads must be positive";
+    case MA_ERR_SEQ_Q: return "seq_len must be positive";
+    case MA_ERR_HEAD_DIM: return "head_dim must be 128";
+    case MA_ERR_SEQ_KV: return "seq_len_kv must be positive";
+    case MA_ERR_PLAN: return "tail plan could not be set up";
+    case MA_ERR_LAYOUT: return "layout must be 0 (bhsd) or 1 (bshd)";
+    case MA_ERR_ROUND_MODE: return "round_mode must be 0 (rtne), 1 (rtna) or 2 (rtz)";
+    case MA_ERR_NULL_POINTER: return "q, k, v and out must not be null";
+    case MA_ERR_ALIGNMENT: return "q, k, v and out must be 16-byte aligned";
+    case MA_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+    case MA_ERR_TENSOR_MAP: return "cuTensorMapEncodeTiled rejected a tensor";
+    case MA_ERR_DRIVER: return "cuTensorMapEncodeTiled not found in the driver";
+    case MA_ERR_DEVICE: return "current CUDA device is not an sm_100 GPU";
+    case MA_ERR_TOO_LARGE: return "problem exceeds the kernel's index range";
+    default: return rc >= MA_ERR_CUDA_BASE ? "CUDA runtime error (code - 1000 is the cudaError_t)" : "unknown error";
+  }
+}
+
+int ma_device_sms(void) {
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return -(MA_ERR_CUDA_BASE + static_cast<int>(e));
+  return sms;
+}
+
+size_t ma_workspace_bytes(int batch, int heads, int seq_len, int seq_len_kv, int num_sms, int flags) {
+  if (check_dims(batch, heads, seq_len, seq_len_kv) != MA_OK) return ma::kStatusBytes;
+  const int sms = resolve_sms(num_sms);
+  if (sms <= 0) return ma::kStatusBytes;
+  const bool split = !(flags & (MA_FLAG_NO_TAIL | MA_FLAG_SIMPLE));
+  return ma::plan_workspace_bytes(ma::plan_tail(batch, heads, seq_len, seq_len_kv, sms, split));
+}
+
+int ma_plan_tail(int batch, int heads, int seq_len, int seq_len_kv, int num_sms, int flags, int plan[8]) {
+  if (plan == nullptr) return MA_ERR_NULL_POINTER;
+  const int rc = check_dims(batch, heads, seq_len, seq_len_kv);
+  if (rc != MA_OK) return rc;
+  const int sms = resolve_sms(num_sms);
+  if (sms <= 0) return sms < 0 ? -sms : MA_ERR_PLAN;
+  const bool split = !(flags & (MA_FLAG_NO_TAIL | MA_FLAG_SIMPLE));
+  const ma::TailPlan t = ma::plan_tail(batch, heads, seq_len, seq_len_kv, sms, split);
+  plan[0] = t.tasks, plan[1] = t.full_units, plan[2] = t.tail_tasks, plan[3] = t.split;
+  plan[4] = t.total_units, plan[5] = t.grid, plan[6] = t.nqb, plan[7] = t.nkb;
+  return MA_OK;
+}
+
+int ma_attention_forward(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                         int seq_len_kv, int head_dim, int layout, int round_mode, void* workspace,
+                         size_t workspace_bytes, int flags, void* stream_) {
+  int rc = check_dims(batch, heads, seq_len, seq_len_kv);
+  if (rc != MA_OK) return rc;
+  if (head_dim != ma::kHeadDim) return MA_ERR_HEAD_DIM;
+  if (layout != MA_LAYOUT_BHSD && layout != MA_LAYOUT_BSHD) return MA_ERR_LAYOUT;
+  if (round_mode < MA_ROUND_RTNE || round_mode > MA_ROUND_RTZ) return MA_ERR_ROUND_MODE;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return MA_ERR_NULL_POINTER;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                         reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
+  if (bits & 15u) return MA_ERR_ALIGNMENT;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  int dev = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (major != 10) return MA_ERR_DEVICE;
+
+  const bool simple = (flags & MA_FLAG_SIMPLE) != 0;
+  const bool want_split = workspace != nullptr && !(flags & MA_FLAG_NO_TAIL) && !simple;
+  const ma::TailPlan plan = ma::plan_tail(batch, heads, seq_len, seq_len_kv, sms, want_split);
+  if (plan.total_units <= 0 || plan.grid <= 0) return MA_ERR_PLAN;
+  if (workspace != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < ma::plan_workspace_bytes(plan))
+      return MA_ERR_WORKSPACE;
+  }
+
+  ma::AttnParams p;
+  std::memset(&p, 0, sizeof(p));
+  rc = make_tensor_map(&p.tm_q, q, batch, heads, seq_len, layout);
+  if (rc == MA_OK) rc = make_tensor_map(&p.tm_k, k, batch, heads, seq_len_kv, layout);
+  if (rc == MA_OK) rc = make_tensor_map(&p.tm_v, v, batch, heads, seq_len_kv, layout);
+  if (rc != MA_OK) return rc;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.status = static_cast<uint32_t*>(workspace);
+  if (workspace != nullptr) {
+    float* parts = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + ma::kStatusBytes);
+    const size_t slots = static_cast<size_t>(plan.tail_tasks) * plan.split;
+    p.part_o = parts;
+    p.part_ml = parts + slots * ma::kPartOFloats;
+  }
+  p.batch = batch, p.heads = heads, p.seq_q = seq_len, p.seq_kv = seq_len_kv;
+  p.bshd = layout, p.round_mode = round_mode;
+  p.nqb = plan.nqb, p.nkb = plan.nkb;
+  p.full_units = plan.full_units, p.tail_tasks = plan.tail_tasks, p.split = plan.split;
+  p.total_units = plan.total_units;
+  // Same constant as the reference (csrc/attention_kernel.hip:59, :1582): log2(e) / sqrt(head_dim), in fp32.
+  p.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(ma::kHeadDim));
+  p.rescale_tau = (flags & MA_FLAG_EXACT_MAX) ? 0.f : 8.f;
+
+  if (workspace != nullptr) {
+    e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+  }
+  if (simple) return cuda_rc(ma::launch_attn_simple(p, stream));
+  e = ma::launch_attn_pipelined(p, plan.grid, stream);
+  if (e == cudaSuccess && plan.tail_tasks > 0) e = ma::launch_merge_parts(p, stream);
+  return cuda_rc(e);
+}
+
+int ma_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, void* stream) {
+  if (round_mode < MA_ROUND_RTNE || round_mode > MA_ROUND_RTZ) return MA_ERR_ROUND_MODE;
+  if (n > 0 && (src == nullptr || dst == nullptr)) return MA_ERR_NULL_POINTER;
+  return cuda_rc(ma::launch_round_bf16(src, dst, n, round_mode, static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

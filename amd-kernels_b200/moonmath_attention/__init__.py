@@ -1,0 +1,21 @@
+"""Dense bf16 flash-attention forward for NVIDIA B200 (sm_100a).
+
+Drop-in for the `forward` entry point of the reference package of the same
+name (moonmath_attention/__init__.py:11-31, moonmath_attention/_kernel.py:14-82):
+
+>>> import torch
+>>> import moonmath_attention as ma
+>>> q = torch.randn(1, 4, 1024, 128, dtype=torch.bfloat16, device="cuda")
+>>> k = torch.randn(1, 4, 1024, 128, dtype=torch.bfloat16, device="cuda")
+>>> v = torch.randn(1, 4, 1024, 128, dtype=torch.bfloat16, device="cuda")
+>>> out = ma.forward(q, k, v)         # torch.bfloat16, same shape
+
+Only the dense forward is provided.  The package talks to the CUDA kernels
+through a ctypes binding of libmoonmath_attention_sm100.so; importing it fails
+if that library has not been built.
+"""
+
+from ._kernel import forward, last_status, plan_tail, workspace_bytes
+from . import _abi as abi
+
+__all__ = ["forward", "plan_tail", "workspace_bytes", "last_status", "abi"]

@@ -1,0 +1,130 @@
+/*
+ * C ABI of libmoonmath_attention_sm100.so: dense bf16 flash-attention forward
+ * for NVIDIA B200 (sm_100a).
+ *
+ * These entry points take the place of the per-rounding-mode native interface
+ * that the reference's torch binding calls (csrc/attention_api.cpp:17-64 and
+ * :122-125 declare it; csrc/attention_kernel.hip:1546-1597 and :1685-1715
+ * define it):
+ *
+ *     int    launch_v_transpose_<mode>(v, v_t, n_rows, seq_len_per_head, heads, layout, stream)
+ *     int    launch_attention_forward_<mode>(q, k, v_t, out, batch, heads, seq_len, seq_len_kv,
+ *                                            head_dim, layout, workspace, stream)
+ *     size_t tail_workspace_bytes_<mode>(void)
+ *
+ * Differences a binding author must know:
+ *   - one library, the rounding mode is an argument (no _rtne/_rtna/_rtz copies);
+ *   - no V pre-transpose pass and no V_t buffer: K and V are read in place in
+ *     either layout;
+ *   - the workspace is sized per problem (ma_workspace_bytes) and starts with a
+ *     256-byte status block that the kernels fill in when a bounded wait gives up;
+ *   - the library keeps no state between calls: calls on different streams or
+ *     devices may run concurrently (the reference keeps a static schedule,
+ *     csrc/attention_kernel.hip:1375-1378).
+ *
+ * All pointers are device pointers on the current CUDA device; `stream` is a
+ * cudaStream_t.  Every call is asynchronous on `stream` and never synchronises.
+ * There is no CPU path: without an sm_100 device the calls fail with an error code.
+ */
+#ifndef MOONMATH_ATTENTION_H_
+#define MOONMATH_ATTENTION_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MA_ABI_VERSION 1
+
+/* layout (reference: csrc/attention_kernel.hip:1581 "0 = BHSD, 1 = BSHD") */
+#define MA_LAYOUT_BHSD 0
+#define MA_LAYOUT_BSHD 1
+
+/* round_mode (reference: BF16Round, csrc/attention_kernel.hip:37-38) */
+#define MA_ROUND_RTNE 0
+#define MA_ROUND_RTNA 1
+#define MA_ROUND_RTZ 2
+
+/* flags */
+#define MA_FLAG_NO_TAIL 0x1      /* never split the last partial round along KV (reference: null workspace /
+                                    MOONMATH_NO_TAIL, csrc/attention_api.cpp:258-267) */
+#define MA_FLAG_SIMPLE 0x2       /* run the serialised cross-check kernel instead of the pipelined one */
+#define MA_FLAG_EXACT_MAX 0x8    /* rescale the accumulator whenever the running maximum rises (tau = 0) */
+
+/* return codes: 1, 2, 3, 5, 6 keep the reference's meaning (csrc/attention_kernel.hip:1573-1576, :1588) */
+#define MA_OK 0
+#define MA_ERR_BATCH_HEADS 1     /* batch <= 0 or heads <= 0 */
+#define MA_ERR_SEQ_Q 2           /* seq_len <= 0 */
+#define MA_ERR_HEAD_DIM 3        /* head_dim != 128 */
+#define MA_ERR_SEQ_KV 5          /* seq_len_kv <= 0 */
+#define MA_ERR_PLAN 6            /* the tail plan could not be set up */
+#define MA_ERR_LAYOUT 7
+#define MA_ERR_ROUND_MODE 8
+#define MA_ERR_NULL_POINTER 9
+#define MA_ERR_ALIGNMENT 10      /* q, k, v, out must be 16-byte aligned */
+#define MA_ERR_WORKSPACE 11      /* workspace smaller than ma_workspace_bytes() or misaligned */
+#define MA_ERR_TENSOR_MAP 12     /* cuTensorMapEncodeTiled refused the tensor */
+#define MA_ERR_DRIVER 13         /* driver entry point not found */
+#define MA_ERR_DEVICE 14         /* current device is not sm_100 */
+#define MA_ERR_TOO_LARGE 15      /* a dimension exceeds what the kernel indexes */
+#define MA_ERR_CUDA_BASE 1000    /* 1000 + cudaError_t of a failed runtime call or launch */
+
+/* Value of MA_ABI_VERSION the library was built with. */
+int ma_abi_version(void);
+
+/* Static text for a return code. */
+const char* ma_error_string(int rc);
+
+/* Number of SMs of the current device, or a negative return code. */
+int ma_device_sms(void);
+
+/*
+ * Bytes of workspace ma_attention_forward needs for this problem on a device
+ * with `num_sms` SMs (<= 0: query the current device).  Always >= 256.
+ * Replaces tail_workspace_bytes (csrc/attention_kernel.hip:1549-1551), which
+ * returns a shape-independent 121 405 440.
+ */
+size_t ma_workspace_bytes(int batch, int heads, int seq_len, int seq_len_kv, int num_sms, int flags);
+
+/*
+ * The tail KV-split decision for a problem (pure host arithmetic; replaces
+ * plan_tail_split, csrc/attention_kernel.hip:1349-1393).  Fills
+ *   plan[0] tasks          256-row query blocks x batch x heads
+ *   plan[1] full_units     tasks run whole
+ *   plan[2] tail_tasks     tasks of the last partial round that are split (0: no split)
+ *   plan[3] split          parts per split task
+ *   plan[4] total_units
+ *   plan[5] grid           CTAs launched
+ *   plan[6] nqb            query blocks per (batch, head)
+ *   plan[7] nkb            128-row key/value blocks
+ */
+int ma_plan_tail(int batch, int heads, int seq_len, int seq_len_kv, int num_sms, int flags, int plan[8]);
+
+/*
+ * out = softmax(q k^T / sqrt(128)) v, bf16 in / bf16 out, fp32 accumulation.
+ * Replaces launch_v_transpose + launch_attention_forward
+ * (csrc/attention_kernel.hip:1560-1597, :1685-1715).
+ *   layout 0: q,out [batch, heads, seq_len, 128], k,v [batch, heads, seq_len_kv, 128]
+ *   layout 1: q,out [batch, seq_len, heads, 128], k,v [batch, seq_len_kv, heads, 128]
+ * All tensors contiguous.  `workspace` may be null (then no KV split and no
+ * status reporting); otherwise it holds at least ma_workspace_bytes(...) bytes,
+ * 256-byte aligned, and its first 256 bytes are cleared by this call and hold
+ * the device status afterwards (word 0 != 0: a kernel gave up, output invalid).
+ */
+int ma_attention_forward(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                         int seq_len_kv, int head_dim, int layout, int round_mode, void* workspace,
+                         size_t workspace_bytes, int flags, void* stream);
+
+/*
+ * dst[i] = bf16 bits of src[i] under round_mode, NaN -> 0x7FFF; device pointers.
+ * Exposes the output rounding of the attention epilogue (reference:
+ * bf16_round_one, csrc/attention_kernel.hip:110-145) for bit-pattern tests.
+ */
+int ma_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOONMATH_ATTENTION_H_ */
