@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of `moonmath_attention.forward` on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c2|c4|c5] [--round-mode rtne|rtna|rtz]
+
+A step is one `forward` call over one batch of synthetic input.  The default
+workload is the headline shape (2, 24, 8192, 128) bf16 BSHD, one whole problem
+per GPU (weak scaling, independent (batch, head) slices, no collective on the
+data path).  `--workload c4` shards the 48 slices of (2, 24, 32768, 128) BHSD
+over the ranks (strong scaling), `--workload c5` is (2, 8, 86016, 128) BSHD.
+
+For N > 1 launch with torch.distributed.run; rank 0 prints one JSON line.
+`--impl reference` times the CPU fp32 oracle (the reference's own fp32 path,
+examples/basic.py:16-17, restated in oracle/oracle.py) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "amd-kernels_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (batch, heads, seq_q, seq_kv, layout, sharded over ranks?)
+    "c2": (2, 24, 8192, 8192, "bshd", False),
+    "c4": (2, 24, 32768, 32768, "bhsd", True),
+    "c5": (2, 8, 86016, 86016, "bshd", False),
+}
+# Reference's published MI300X figures for (2,24,8192,128): README.md:98-100 -> 4*B*H*S^2*D / t.
+PUBLISHED_TFLOPS = {"rtne": 535.0, "rtna": 545.8, "rtz": 552.9}
+# dram__bytes_read.sum + dram__bytes_write.sum of one attn_pipelined_kernel launch at the c2 shape
+# (profiles/ncu_attn_pipelined_c2.md); None until a capture exists.
+NCU_TRAFFIC_BYTES = {"c2": None}
+
+
+def measured_peaks() -> tuple[float, float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples (SM clock, throttle reasons) while the timed regions run."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(self.gpu_index)],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        clocks, reasons, mx, power = [], set(), None, []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                clocks.append(float(f[1]))
+                mx = float(f[2])
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if clocks:
+            # samples taken under load: the upper half by power draw
+            busy = [c for c, p in zip(clocks, power) if p >= statistics.median(power)]
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=mx, reasons=sorted(reasons), samples=len(clocks),
+                       power_w_max=max(power))
+        return out
+
+
+def dist_setup(n_gpus: int):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier(world: int) -> None:
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def make_device_inputs(shape_q, shape_kv, dev, seed):
+    g = torch.Generator(device=dev)
+    g.manual_seed(seed)
+    mk = lambda s: torch.randn(s, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)  # noqa: E731
+    return mk(shape_q), mk(shape_kv), mk(shape_kv)
+
+
+def cpu_oracle_rate(seq_kv: int, max_rows: int, budget_s: float, threads: int) -> dict:
+    """Times the CPU fp32 oracle on query-row samples of one (batch, head) slice of the workload."""
+    from oracle import oracle as orc
+
+    torch.set_num_threads(threads)
+    k = orc.make_slice(seq_kv, 0, 1)[None, None]
+    v = orc.make_slice(seq_kv, 0, 2)[None, None]
+    rows = 512
+    q = orc.make_slice(rows, 0, 0)[None, None]
+    orc.attention_fp32(q, k, v, "bhsd")  # warm-up (thread pool, page faults)
+    t0 = time.perf_counter()
+    orc.attention_fp32(q, k, v, "bhsd")
+    probe = time.perf_counter() - t0
+    rows_budget = int(max(rows, min(max_rows, rows * budget_s / max(probe, 1e-4))))
+    rows_budget = (rows_budget // 512) * 512
+    q = orc.make_slice(rows_budget, 0, 0)[None, None]
+    t0 = time.perf_counter()
+    orc.attention_fp32(q, k, v, "bhsd")
+    dt = time.perf_counter() - t0
+    flops = 4.0 * rows_budget * seq_kv * 128
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+            "sample": f"{rows_budget} of the workload's {max_rows} query rows (batch x heads x seq) against {seq_kv} keys, "
+                      f"fp32 torch CPU oracle, {dt:.2f} s", "seconds": dt, "rows": rows_budget}
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    """The reference arm: the CPU oracle on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    B, H, Sq, Skv, layout, _ = WORKLOADS[args.workload]
+    threads = os.cpu_count() or 1
+    total_budget = 150.0
+    per_step = total_budget / max(1, args.steps + args.warmup)
+    from oracle import oracle as orc
+
+    torch.set_num_threads(threads)
+    k = orc.make_slice(Skv, 0, 1)[None, None]
+    v = orc.make_slice(Skv, 0, 2)[None, None]
+    probe_rows = 256
+    q = orc.make_slice(probe_rows, 0, 0)[None, None]
+    orc.attention_fp32(q, k, v, "bhsd")
+    t0 = time.perf_counter()
+    orc.attention_fp32(q, k, v, "bhsd")
+    probe = time.perf_counter() - t0
+    rows = int(max(128, min(Sq, probe_rows * per_step / max(probe, 1e-4))))
+    rows = max(128, (rows // 128) * 128)
+    q = orc.make_slice(rows, 0, 0)[None, None]
+    for _ in range(args.warmup):
+        orc.attention_fp32(q, k, v, "bhsd")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        orc.attention_fp32(q, k, v, "bhsd")
+    dt = (time.perf_counter() - t0) / max(1, args.steps)
+    flops = 4.0 * rows * Skv * 128
+    val = flops / dt / 1e12
+    sample = f"{rows} query rows x {Skv} keys of one (batch, head) slice per step, fp32 torch CPU oracle"
+    line = {
+        "impl": "reference", "metric": "TFLOP/s per ma.forward (4*B*H*Sq*Skv*D flops)", "value": val,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic N(0,1), seeded",
+        "config": {"workload": f"{args.workload} ({B},{H},{Sq},{Skv},128) {layout}", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--round-mode", default="rtne", choices=["rtne", "rtna", "rtz"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        run_reference(args, rank, int(os.environ.get("WORLD_SIZE", "1")))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; moonmath_attention has no CPU path")
+    import moonmath_attention as ma
+    from moonmath_attention.shard import max_over_ranks, slice_range
+
+    rank, world, local = dist_setup(args.gpus)
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    warmup = max(3, args.warmup)
+
+    B, H, Sq, Skv, layout, sharded = WORKLOADS[args.workload]
+    if sharded:
+        mine = slice_range(rank, world, B * H)
+        b_loc, h_loc = 1, len(mine)
+        scaling = "strong"
+    else:
+        b_loc, h_loc = B, H
+        scaling = "weak"
+    shape = (lambda S: (b_loc, S, h_loc, 128)) if layout == "bshd" else (lambda S: (b_loc, h_loc, S, 128))
+    q, k, v = make_device_inputs(shape(Sq), shape(Skv), dev, seed=42 * 1000003 + rank)
+    out = torch.empty_like(q)
+    flops_rank = 4.0 * b_loc * h_loc * Sq * Skv * 128
+    flops_total = flops_rank * world if not sharded else 4.0 * B * H * Sq * Skv * 128
+    plan = ma.plan_tail(b_loc, h_loc, Sq, Skv, torch.cuda.get_device_properties(dev).multi_processor_count)
+    launches_per_step = 1 + (1 if plan["tail_tasks"] else 0)
+
+    def step():
+        ma.forward(q, k, v, out=out, round_mode=args.round_mode, layout=layout)
+
+    sampler = ClockSampler(local)
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier(world)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier(world)
+    ms_rank = e0.elapsed_time(e1) / args.steps
+    status = ma.last_status()
+    ms = max_over_ranks(ms_rank)
+
+    # the other rounding modes, a shorter loop each (same inputs)
+    modes = {}
+    for mode in ("rtne", "rtna", "rtz"):
+        for _ in range(3):
+            ma.forward(q, k, v, out=out, round_mode=mode, layout=layout)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        n = max(10, args.steps // 4)
+        for _ in range(n):
+            ma.forward(q, k, v, out=out, round_mode=mode, layout=layout)
+        b.record()
+        torch.cuda.synchronize()
+        modes[mode] = max_over_ranks(a.elapsed_time(b) / n)
+
+    # end to end: pinned host buffers, H2D of q, k, v and D2H of the result inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        hq, hk, hv = (t.cpu().pin_memory() for t in (q, k, v))
+        hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+
+        def e2e_step():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            ma.forward(dq, dk, dv, out=out, round_mode=args.round_mode, layout=layout)
+            hout.copy_(out, non_blocking=True)
+
+        n_e2e = max(3, min(args.steps, 20))
+        for _ in range(2):
+            e2e_step()
+        barrier(world)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n_e2e):
+            e2e_step()
+        b.record()
+        barrier(world)
+        e2e_ms = max_over_ranks(a.elapsed_time(b) / n_e2e)
+        e2e = {"value": flops_total / e2e_ms / 1e9, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": (hq.numel() + hk.numel() + hv.numel()) * 2,
+               "d2h_bytes_per_step": hout.numel() * 2, "steps": n_e2e}
+    clocks = sampler.stop() if rank == 0 else None
+
+    if rank != 0:
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.destroy_process_group()
+        return
+
+    peak, peak_sustained, peak_src = measured_peaks()
+    achieved = flops_rank / ms_rank / 1e9
+    line = {
+        "metric": "TFLOP/s per ma.forward (4*B*H*Sq*Skv*D flops)",
+        "value": flops_total / ms / 1e9,
+        "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": scaling,
+        "vs_baseline": (flops_total / ms / 1e9) / PUBLISHED_TFLOPS[args.round_mode] if args.workload == "c2" else None,
+        "dtype": "bf16", "data": "synthetic N(0,1) drawn in fp32, cast to bf16, seeded per rank",
+        "config": {"workload": f"{args.workload} ({B},{H},{Sq},{Skv},128) {layout}"
+                               + (f", {B * H} slices sharded over {world} ranks" if sharded else " per GPU"),
+                   "round_mode": args.round_mode, "l2": "inputs + output larger than L2 (no flush needed)",
+                   "tail_plan": plan, "baseline_hw": "vs_baseline divides by the reference's MI300X figure"},
+        "ms_by_round_mode": modes,
+        "pct_of_peak": {"burst": 100 * achieved / peak, "sustained": 100 * achieved / peak_sustained},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload),
+                     "peak_source": f"{peak_src} bf16_tflops (burst); sustained {peak_sustained}",
+                     "flops_per_launch": flops_rank},
+        "gpu_launches": launches_per_step * args.steps,
+        "device_status": status[:3],
+        "clocks": clocks,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu_oracle_rate(Skv, B * H * Sq, 12.0, torch.get_num_threads())
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

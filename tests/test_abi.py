@@ -1,0 +1,67 @@
+"""The C ABI without a GPU: the library loads, exports what the header declares, validates arguments."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import moonmath_attention as ma
+from moonmath_attention import _abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "moonmath_attention.h")
+
+
+def _declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(ma_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    syms = _declared_symbols()
+    assert set(syms) == set(_abi.EXPORTS)
+    lib = ctypes.CDLL(str(_abi.LIB_PATH))
+    for s in syms:
+        assert hasattr(lib, s), s
+
+
+def test_abi_version_and_error_strings():
+    assert _abi.lib.ma_abi_version() == 1
+    m = re.search(r"#define MA_ABI_VERSION (\d+)", open(HEADER).read())
+    assert int(m.group(1)) == _abi.ABI_VERSION
+    for rc in (0, 1, 2, 3, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 1001):
+        assert _abi.error_string(rc)
+    assert "unknown" in _abi.error_string(4)
+
+
+def _call(q=16, k=16, v=16, out=16, B=1, H=1, Sq=128, Skv=128, D=128, layout=0, mode=0, ws=0, wsb=0, flags=0):
+    return _abi.lib.ma_attention_forward(q, k, v, out, B, H, Sq, Skv, D, layout, mode, ws, wsb, flags, 0)
+
+
+def test_argument_validation_return_codes():
+    """Codes 1, 2, 3, 5 as the reference's launcher (csrc/attention_kernel.hip:1573-1576); checks run before any CUDA call."""
+    assert _call(B=0) == 1 and _call(H=-1) == 1
+    assert _call(Sq=0) == 2
+    assert _call(Skv=0) == 5
+    assert _call(D=64) == 3
+    assert _call(layout=2) == 7
+    assert _call(mode=3) == 8
+    assert _call(q=0) == 9 and _call(out=0) == 9
+    assert _call(k=24) == 10
+    assert _call(B=70000) == 15
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour of a machine without a GPU")
+def test_no_gpu_means_an_error_not_a_fallback():
+    rc = _call()
+    assert rc >= 1000, "a valid call without a CUDA device must fail with a CUDA error code"
+    q = torch.zeros(1, 1, 8, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ma.forward(q, q, q)
+
+
+def test_round_bf16_rejects_bad_arguments():
+    assert _abi.lib.ma_round_bf16(0, 0, 0, 5, 0) == 8
+    assert _abi.lib.ma_round_bf16(0, 0, 4, 0, 0) == 9
