@@ -73,8 +73,8 @@ __device__ __forceinline__ void record_error(uint32_t* status, uint32_t code, ui
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (sm100::mbar_try_wait(bar, parity)) return true;
-    if ((it & 0x3FFu) == 0u) {
+    if (sm100::mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if ((it & 0x3Fu) == 0u) {
       if (*ctx.abort) return false;
       if (ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
         *ctx.abort = 1;
@@ -132,6 +132,57 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Three-input maximum; NaN in any operand gives NaN (so a row maximum doubles as a NaN detector).
+__device__ __forceinline__ float fmax3_nan(float a, float b, float c) {
+  float d;
+  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// Packed pairs of fp32 in a 64-bit register: the FMA pipe of sm_100 processes both halves in one instruction.
+using f32x2 = uint64_t;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// 2^x for a pair on the FMA pipe instead of the special-function unit: x is clamped to >= -126,
+// split as n + f with n = round(x), f in [-1/2, 1/2]; 2^f by a degree-3 minimax polynomial
+// (maximum relative error 7.5e-5, far below the 2^-9 of the bf16 rounding applied to P afterwards);
+// n goes straight into the exponent field.  Valid for finite x <= 127 and x = -inf (gives ~2^-126);
+// NaN must not reach it: callers route rows with a non-finite maximum to ex2_approx.
+__device__ __forceinline__ void ex2_poly2(f32x2 x, float& p0, float& p1) {
+  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
+  float x0, x1;
+  unpack2(x, x0, x1);
+  const f32x2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const f32x2 xr = add2(xc, pack2(kMagic, kMagic));
+  const f32x2 nf = add2(xr, pack2(-kMagic, -kMagic));
+  const f32x2 f = fma2(nf, pack2(-1.f, -1.f), xc);
+  f32x2 p = fma2(f, pack2(0.05517132207751274f, 0.05517132207751274f), pack2(0.24261054396629333f, 0.24261054396629333f));
+  p = fma2(p, f, pack2(0.6932609677314758f, 0.6932609677314758f));
+  p = fma2(p, f, pack2(0.9999281167984009f, 0.9999281167984009f));
+  float r0, r1, q0, q1;
+  unpack2(xr, r0, r1);
+  unpack2(p, q0, q1);
+  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+
 // Packs two probabilities as bf16 for the P operand of the second MMA (`lo` has the lower key index).
 // The tensor core takes A and B of one 16-bit format only: a kind::f16 MMA with fp16 A and bf16 B is
 // an illegal instruction on sm_100, so P shares V's bf16.  P is rounded to nearest-even in every
@@ -187,22 +238,46 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* t
   tma_load_tile_half(dst + kTileBytes / 2, tm, bar, bshd, 64, row0, h, b);
 }
 
-// S[128 x 128] = A_tile (K-major) * B_tile^T (K-major): 8 MMAs of K = 16 over the head dimension.
-__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_smem, uint32_t k_smem) {
+// ---------------------------------------------------------------------------
+// MMA issue.  One thread issues every tcgen05.mma of a CTA, and that thread's
+// instruction stream is the pace-maker of the kernel: descriptors are therefore
+// split into a constant high word and a low word that is a 32-bit add away from
+// a per-tile base computed once.
+//   low word : [0,14) start address >> 4, [16,30) leading byte offset >> 4
+//   high word: [0,14) stride byte offset >> 4, [14,16) version = 1, [29,32) swizzle = 2 (128 bytes)
+// ---------------------------------------------------------------------------
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);                 // SBO = 1024 bytes
+constexpr uint32_t kDescLoKMajor = (16u >> 4) << 16;                                 // LBO unused (1)
+constexpr uint32_t kDescLoMnMajor = (static_cast<uint32_t>(kTileBytes / 2) >> 4) << 16;  // LBO = 16 KiB: next 64 columns
+
+// Low descriptor word of a tile at shared address `smem` read as a K-major operand (Q, K) ...
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem) { return ((smem & 0x3FFFFu) >> 4) | kDescLoKMajor; }
+// ... or as an MN-major operand (V: head dimension contiguous).
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem) { return ((smem & 0x3FFFFu) >> 4) | kDescLoMnMajor; }
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHi));
+  return d;
+}
+
+// S[128 x 128] = Q_tile * K_tile^T, both K-major: 8 MMAs of K = 16 over the head dimension.
+// k-step ks lives in 64-column half (ks >> 2), 32 bytes per step inside the 128-byte swizzle row.
+__device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo) {
   constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 0, kTileM, kTileN);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t off = (ks >> 2) * (kTileBytes / 2) + (ks & 3) * 32;
-    sm100::umma_ss(d_tmem, sm100::umma_smem_desc(q_smem + off, 16, 1024), sm100::umma_smem_desc(k_smem + off, 16, 1024),
-                   idesc, ks > 0 ? 1u : 0u);
+    const uint32_t off = ((ks >> 2) * (kTileBytes / 2) + (ks & 3) * 32) >> 4;
+    sm100::umma_ss(d_tmem, make_desc(q_lo + off), make_desc(k_lo + off), idesc, ks > 0 ? 1u : 0u);
   }
 }
-// O[128 x 128] (+)= P (TMEM, 16-bit pairs) * V_tile (MN-major: head dim contiguous): 8 MMAs of K = 16 keys.
-__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_smem, bool accumulate) {
+// O[128 x 128] (+)= P (TMEM, bf16 pairs, 8 columns per step) * V_tile (MN-major): 8 MMAs of K = 16 keys,
+// 16 key rows = 2048 bytes per step.
+__device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo, bool accumulate) {
   constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 1, kTileM, kHeadDim);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    sm100::umma_ts(d_tmem, p_tmem + ks * 8, sm100::umma_smem_desc(v_smem + ks * 2048, kTileBytes / 2, 1024), idesc,
+    sm100::umma_ts(d_tmem, p_tmem + ks * 8, make_desc(v_lo + ks * (2048 >> 4)), idesc,
                    (accumulate || ks > 0) ? 1u : 0u);
   }
 }

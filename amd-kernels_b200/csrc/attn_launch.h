@@ -16,7 +16,8 @@ struct AttnParams;
 cudaError_t launch_attn_simple(const AttnParams& p, cudaStream_t stream);
 
 // Persistent warp-specialised kernel; `grid` CTAs walk the unit list of the plan.
-cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, cudaStream_t stream);
+// `poly_of_4`: of every four score pairs, how many take the polynomial 2^x (rest: special-function unit).
+cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, int poly_of_4, cudaStream_t stream);
 
 // Combines the partial results of KV-split tasks into the bf16 output.
 cudaError_t launch_merge_parts(const AttnParams& p, cudaStream_t stream);

@@ -85,6 +85,19 @@ __device__ __forceinline__ Unit decode_unit(const AttnParams& p, int u) {
   return r;
 }
 
+#ifdef MA_TRACE
+// Development-only timestamp trace (built into a separate library, never into the product build).
+__device__ unsigned long long g_trace[8192];
+#define MA_TRACE_AT(slot, cond)                                            \
+  do {                                                                     \
+    if ((cond) && blockIdx.x == 0 && (slot) < 8192) g_trace[(slot)] = clock64(); \
+  } while (0)
+#else
+#define MA_TRACE_AT(slot, cond) \
+  do {                          \
+  } while (0)
+#endif
+
 #define MA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), (site), ctx)) return
 #define MA_WAIT_WARP(bar, parity, site) \
@@ -128,8 +141,10 @@ __device__ __forceinline__ void role_producer(const AttnParams& p, uint32_t base
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
   const uint32_t bars = base + kOffBars;
-  const uint32_t sQ0 = base + kOffQ, sQ1 = sQ0 + kTileBytes;
-  const uint32_t tS0 = tmem, tS1 = tmem + 128, tO0 = tmem + 256, tO1 = tmem + 384;
+  const uint32_t q_lo = desc_lo_kmajor(base + kOffQ);      // + tile  * (kTileBytes >> 4)
+  const uint32_t kv_lo_k = desc_lo_kmajor(base + kOffKV);  // + stage * (kTileBytes >> 4)
+  const uint32_t kv_lo_v = desc_lo_mnmajor(base + kOffKV);
+  constexpr uint32_t kTileLo = kTileBytes >> 4;
   uint32_t fill = 0;   // K/V ring fills consumed before this unit
   uint32_t it = 0;     // units so far
   uint32_t blk = 0;    // key/value blocks so far (phase of s_full / p_full)
@@ -138,52 +153,52 @@ __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uin
     const int n = un.kb_end - un.kb_begin;
 
     // S0(0), S1(0)
-    MA_WAIT(bars + 8 * (kBarQFull + 0), it & 1, 0x20);
     {
-      const uint32_t f = fill, st = f % kStages;
-      MA_WAIT(bars + 8 * (kBarKvFull + st), (f / kStages) & 1, 0x21);
-      tc_fence_after_sync();
-      const uint32_t sK = base + kOffKV + st * kTileBytes;
-      issue_qk(tS0, sQ0, sK);
-      umma_commit(bars + 8 * (kBarSFull + 0));
-      MA_WAIT(bars + 8 * (kBarQFull + 1), it & 1, 0x22);
-      issue_qk(tS1, sQ1, sK);
-      umma_commit(bars + 8 * (kBarSFull + 1));
+      const uint32_t st = fill % kStages;
+      MA_WAIT(bars + 8 * (kBarKvFull + st), (fill / kStages) & 1, 0x21);
+      const uint32_t k_lo = kv_lo_k + st * kTileLo;
+#pragma unroll 1
+      for (uint32_t t = 0; t < 2; ++t) {
+        MA_WAIT(bars + 8 * (kBarQFull + t), it & 1, 0x20 + t);
+        tc_fence_after_sync();
+        issue_qk(tmem + t * 128, q_lo + t * kTileLo, k_lo);
+        umma_commit(bars + 8 * (kBarSFull + t));
+      }
       umma_commit(bars + 8 * (kBarKvEmpty + st));
       if (n == 1) umma_commit(bars + 8 * kBarQEmpty);
     }
     for (int j = 0; j < n; ++j, ++blk) {
       const uint32_t fv = fill + 2 * j + 1, sv = fv % kStages;   // V(j)
       const uint32_t fk = fill + 2 * j + 2, sk = fk % kStages;   // K(j+1)
-      const uint32_t sV = base + kOffKV + sv * kTileBytes;
-      const uint32_t sK = base + kOffKV + sk * kTileBytes;
+      const uint32_t v_lo = kv_lo_v + sv * kTileLo;
+      const uint32_t k_lo = kv_lo_k + sk * kTileLo;
       const bool more = (j + 1 < n);
-
-      // O0 (+)= P0(j) V(j)
+      const bool tr = it == 0 && j < 40;
+      const int tslot = 2000 + j * 8;
+      MA_TRACE_AT(tslot + 0, tr);
+      // Operand tiles first: these waits are normally long satisfied and must not sit between
+      // "P is ready" and the issue of the MMAs that consume it.
       MA_WAIT(bars + 8 * (kBarKvFull + sv), (fv / kStages) & 1, 0x23);
-      MA_WAIT(bars + 8 * (kBarPFull + 0), blk & 1, 0x24);
-      if (j == 0 && it > 0) MA_WAIT(bars + 8 * (kBarOFree + 0), (it - 1) & 1, 0x25);
-      tc_fence_after_sync();
-      issue_pv(tO0, tS0, sV, j > 0);
-      if (!more) umma_commit(bars + 8 * (kBarOFull + 0));
-      // S0(j+1)
-      if (more) {
-        MA_WAIT(bars + 8 * (kBarKvFull + sk), (fk / kStages) & 1, 0x26);
+      if (more) MA_WAIT(bars + 8 * (kBarKvFull + sk), (fk / kStages) & 1, 0x26);
+      MA_TRACE_AT(tslot + 1, tr);
+#pragma unroll 1
+      for (uint32_t t = 0; t < 2; ++t) {
+        // O_t (+)= P_t(j) V(j);  S_t(j+1) = Q_t K(j+1)^T
+        if (j == 0 && it > 0) MA_WAIT(bars + 8 * (kBarOFree + t), (it - 1) & 1, 0x25);
+        MA_WAIT(bars + 8 * (kBarPFull + t), blk & 1, 0x24);
+        MA_TRACE_AT(tslot + 2 + 2 * t, tr);
         tc_fence_after_sync();
-        issue_qk(tS0, sQ0, sK);
-        umma_commit(bars + 8 * (kBarSFull + 0));
+        issue_pv(tmem + 256 + t * 128, tmem + t * 128, v_lo, j > 0);
+        if (t == 1) umma_commit(bars + 8 * (kBarKvEmpty + sv));
+        if (more) {
+          issue_qk(tmem + t * 128, q_lo + t * kTileLo, k_lo);
+          umma_commit(bars + 8 * (kBarSFull + t));
+        } else {
+          umma_commit(bars + 8 * (kBarOFull + t));
+        }
+        MA_TRACE_AT(tslot + 3 + 2 * t, tr);
       }
-      // O1 (+)= P1(j) V(j)
-      MA_WAIT(bars + 8 * (kBarPFull + 1), blk & 1, 0x27);
-      if (j == 0 && it > 0) MA_WAIT(bars + 8 * (kBarOFree + 1), (it - 1) & 1, 0x28);
-      tc_fence_after_sync();
-      issue_pv(tO1, tS1, sV, j > 0);
-      umma_commit(bars + 8 * (kBarKvEmpty + sv));
-      if (!more) umma_commit(bars + 8 * (kBarOFull + 1));
-      // S1(j+1)
       if (more) {
-        issue_qk(tS1, sQ1, sK);
-        umma_commit(bars + 8 * (kBarSFull + 1));
         umma_commit(bars + 8 * (kBarKvEmpty + sk));
         if (j + 2 == n) umma_commit(bars + 8 * kBarQEmpty);
       }
@@ -194,20 +209,27 @@ __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uin
 
 // Reads this thread's 128 scores of the current block; keys past the end of the sequence become -inf.
 __device__ __forceinline__ void load_scores(uint32_t tS, uint32_t (&s)[128], int valid) {
-  tmem_ld32_at<0>(tS, s);
-  tmem_ld32_at<32>(tS + 32, s);
-  tmem_ld32_at<64>(tS + 64, s);
-  tmem_ld32_at<96>(tS + 96, s);
-  tmem_ld_wait32_at<0>(s);
-  tmem_ld_wait32_at<32>(s);
-  tmem_ld_wait32_at<64>(s);
-  tmem_ld_wait32_at<96>(s);
+  tmem_ld128_sync(tS, s);
   if (valid < kTileN) {
 #pragma unroll
     for (int i = 0; i < 128; ++i)
       if (i >= valid) s[i] = __float_as_uint(-INFINITY);
   }
 }
+// Row maximum that is NaN when any score is NaN (and +inf / -inf when the row holds them): one
+// instruction per two scores, and the result tells whether the row needs the exact slow path.
+__device__ __forceinline__ float row_max_nan(const uint32_t (&s)[128]) {
+  float mx[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) mx[c] = fmax3_nan(__uint_as_float(s[16 * c]), __uint_as_float(s[16 * c + 1]), -INFINITY);
+#pragma unroll
+  for (int i = 1; i < 8; ++i)
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      mx[c] = fmax3_nan(mx[c], __uint_as_float(s[16 * c + 2 * i]), __uint_as_float(s[16 * c + 2 * i + 1]));
+  return fmax3_nan(fmax3_nan(mx[0], mx[1], mx[2]), fmax3_nan(mx[3], mx[4], mx[5]), fmax3_nan(mx[6], mx[7], mx[7]));
+}
+// Row maximum that ignores NaN scores (fmaxf semantics), for the slow path.
 __device__ __forceinline__ float row_max(const uint32_t (&s)[128]) {
   float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
@@ -223,6 +245,7 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[128]) {
 // ---------------------------------------------------------------------------
 // softmax warps (128 threads per tile, one query row each)
 // ---------------------------------------------------------------------------
+template <int kPolyOf4>
 __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem, uint32_t base, uint32_t tmem, int tile,
                                              int row, const WaitCtx& ctx) {
   const uint32_t bars = base + kOffBars;
@@ -238,12 +261,22 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
     const int n = un.kb_end - un.kb_begin;
     float m_ref = 0.f, l_run = 0.f;
     for (int j = 0; j < n; ++j, ++blk) {
+      const bool tr = (row == 0) && it == 0 && j < 40;
+      const int tslot = tile * 1000 + j * 8;
+      MA_TRACE_AT(tslot + 0, tr);
       MA_WAIT_WARP(bar_s, blk & 1, 0x30 + tile);
+      MA_TRACE_AT(tslot + 1, tr);
       tc_fence_after_sync();
       uint32_t s[128];
       const int valid = p.seq_kv - (un.kb_begin + j) * kTileN;
       load_scores(tS, s, valid);
-      const float m_blk = row_max(s) * scale;
+      // Fast path: every score of every row of this warp is finite or -inf (masked / excluded keys).
+      // Otherwise (a NaN or +inf score somewhere, or a row of -inf only) the whole warp takes the
+      // slow path, whose arithmetic propagates NaN and infinities exactly as IEEE arithmetic does.
+      MA_TRACE_AT(tslot + 2, tr);
+      float m_blk = row_max_nan(s) * scale;
+      const bool slow = __any_sync(0xffffffffu, !(fabsf(m_blk) < INFINITY));
+      if (slow) m_blk = row_max(s) * scale;
 
       if (j == 0) {
         // First block of the unit: the accumulator is overwritten, nothing to rescale.
@@ -259,8 +292,7 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
 #pragma unroll 1
           for (int c = 0; c < 4; ++c) {
             uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
-            tmem_ld_wait32(o);
+            tmem_ld32_sync(tO + c * 32, o);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
             tmem_st32(tO + c * 32, o);
@@ -270,23 +302,68 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
         }
       }
 
-      // p = 2^(s * scale - m_ref); the row sum uses the unrounded values; P is packed in place:
-      // s[i] <- (p[2i], p[2i+1]) for i ascending never overwrites a score that is still needed.
-      float sum0 = 0.f, sum1 = 0.f;
+      MA_TRACE_AT(tslot + 3, tr);
+      // p = 2^(s * scale - m_ref); the row sum uses the unrounded values.  P goes out in four chunks of
+      // 32 keys (16 packed registers each) over the first 64 columns of S, whose scores are all in
+      // registers by now.
+      if (!slow) {
+        const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), scale, -m_ref));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), scale, -m_ref));
-        sum0 += p0;
-        sum1 += p1;
-        s[i] = pack_p(p0, p1);
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int e = 32 * c + 2 * i;
+            float p0, p1;
+            if (kPolyOf4 == 5) {  // experiment: no packed arithmetic at all
+              p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale, -m_ref));
+              p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale, -m_ref));
+              sum[(2 * i) & 3] += p0;
+              sum[(2 * i + 1) & 3] += p1;
+              pk[i] = pack_p(p0, p1);
+              continue;
+            }
+            const f32x2 x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
+            if ((i & 3) < kPolyOf4) {
+              ex2_poly2(x, p0, p1);  // FMA pipe
+            } else {
+              float x0, x1;
+              unpack2(x, x0, x1);
+              p0 = ex2_approx(x0);  // special-function unit
+              p1 = ex2_approx(x1);
+            }
+            sum[(2 * i) & 3] += p0;
+            sum[(2 * i + 1) & 3] += p1;
+            pk[i] = pack_p(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+      } else {
+        float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int e = 32 * c + 2 * i;
+            const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale, -m_ref));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale, -m_ref));
+            sum0 += p0;
+            sum1 += p1;
+            pk[i] = pack_p(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        l_run += sum0 + sum1;
       }
-      l_run += sum0 + sum1;
-      tmem_st32_at<0>(tS, s);
-      tmem_st32_at<32>(tS + 32, s);
+      MA_TRACE_AT(tslot + 4, tr);
       tmem_st_wait();
+      MA_TRACE_AT(tslot + 5, tr);
       tc_fence_before_sync();
       mbar_arrive(bar_p);
+      MA_TRACE_AT(tslot + 6, tr);
     }
     // The epilogue must have consumed the previous unit's l_ready phase before this one
     // completes; with single-block units nothing else orders the two.
@@ -325,8 +402,7 @@ __device__ __forceinline__ void role_epilogue(const AttnParams& p, uint8_t* smem
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(tO + c * 32, o);
-          tmem_ld_wait32(o);
+          tmem_ld32_sync(tO + c * 32, o);
           if (live) store_chunk_bf16(p.round_mode, dst + c * 32, o, inv);
         }
       } else {
@@ -335,8 +411,7 @@ __device__ __forceinline__ void role_epilogue(const AttnParams& p, uint8_t* smem
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t o[32];
-          tmem_ld32(tO + c * 32, o);
-          tmem_ld_wait32(o);
+          tmem_ld32_sync(tO + c * 32, o);
 #pragma unroll
           for (int q = 0; q < 8; ++q)
             dst[c * 8 + q] = make_float4(__uint_as_float(o[4 * q]), __uint_as_float(o[4 * q + 1]),
@@ -350,6 +425,7 @@ __device__ __forceinline__ void role_epilogue(const AttnParams& p, uint8_t* smem
   }
 }
 
+template <int kPolyOf4>
 __global__ void __launch_bounds__(kThreads, 1) attn_pipelined_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -385,13 +461,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_pipelined_kernel(const __gri
   const uint32_t tmem = *tmem_slot;
 
   if (warp < 8) {
-    setmaxnreg_inc<176>();
-    role_softmax(p, smem, base, tmem, warp >> 2, tid & 127, ctx);
+    setmaxnreg_inc<192>();
+    role_softmax<kPolyOf4>(p, smem, base, tmem, warp >> 2, tid & 127, ctx);
   } else if (warp < 12) {
-    setmaxnreg_dec<96>();
+    setmaxnreg_dec<80>();
     role_epilogue(p, smem, base, tmem, tid & 127, ctx);
   } else {
-    setmaxnreg_dec<64>();
+    setmaxnreg_dec<48>();
     if (warp == 12 && lane == 0) role_mma(p, base, tmem, ctx);
     if (warp == 13 && lane == 0) role_producer(p, base, ctx);
   }
@@ -403,8 +479,22 @@ __global__ void __launch_bounds__(kThreads, 1) attn_pipelined_kernel(const __gri
 
 }  // namespace
 
-cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, cudaStream_t stream) {
-  auto kernel = attn_pipelined_kernel;
+#ifdef MA_TRACE
+extern "C" int ma_trace_read(unsigned long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * n));
+}
+#endif
+
+cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, int poly_of_4, cudaStream_t stream) {
+  auto kernel = attn_pipelined_kernel<2>;
+  switch (poly_of_4) {
+    case 0: kernel = attn_pipelined_kernel<0>; break;
+    case 1: kernel = attn_pipelined_kernel<1>; break;
+    case 3: kernel = attn_pipelined_kernel<3>; break;
+    case 4: kernel = attn_pipelined_kernel<4>; break;
+    case 5: kernel = attn_pipelined_kernel<5>; break;
+    default: break;
+  }
   cudaError_t e =
       cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
   if (e != cudaSuccess) return e;

@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
     if (!ok) break;
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_qk(tS, sQ, sK);
+      issue_qk(tS, desc_lo_kmajor(sQ), desc_lo_kmajor(sK));
       umma_commit(bar_mma);
     }
     ok = mbar_wait_warp(bar_mma, mma_phase, 3, ctx);
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
 
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_pv(tO, tS, sV, j > 0);
+      issue_pv(tO, tS, desc_lo_mnmajor(sV), j > 0);
       umma_commit(bar_mma);
     }
     ok = mbar_wait_warp(bar_mma, mma_phase, 4, ctx);

@@ -183,7 +183,8 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
     if (e != cudaSuccess) return cuda_rc(e);
   }
   if (simple) return cuda_rc(ma::launch_attn_simple(p, stream));
-  e = ma::launch_attn_pipelined(p, plan.grid, stream);
+  const int poly = (flags & 0x800) ? ((flags >> 8) & 7) : 2;  // bits 8-11: tuning override
+  e = ma::launch_attn_pipelined(p, plan.grid, poly, stream);
   if (e == cudaSuccess && plan.tail_tasks > 0) e = ma::launch_merge_parts(p, stream);
   return cuda_rc(e);
 }

@@ -25,6 +25,7 @@ def _flags_from_env() -> int:
         flags |= _abi.FLAG_SIMPLE
     if os.environ.get("MOONMATH_EXACT_MAX"):
         flags |= _abi.FLAG_EXACT_MAX
+    flags |= int(os.environ.get("MOONMATH_FLAGS", "0"), 0)  # raw flag bits (tuning)
     return flags
 
 
