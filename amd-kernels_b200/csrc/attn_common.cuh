@@ -32,7 +32,8 @@ constexpr uint32_t kErrWaitTimeout = 0x57A17u;
 constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 
 struct AttnParams {
-  CUtensorMap tm_q, tm_k, tm_v;  // rank-4 maps, box = 64 head-dim elements x 128 rows, 128-byte swizzle
+  // rank-4 maps, 128-byte swizzle, box = 64 head-dim elements x 128 rows (Q) or x the kernel's key block rows (K, V)
+  CUtensorMap tm_q, tm_k, tm_v;
   __nv_bfloat16* out;
   uint32_t* status;  // may be null
   float* part_o;     // [slots][256][128] un-normalised fp32 partial outputs of KV-split units
@@ -231,11 +232,12 @@ __device__ __forceinline__ void tma_load_tile_half(uint32_t dst, const CUtensorM
     sm100::tma_load_4d(dst, tm, bar, d0, row0, h, b);
   }
 }
-// A whole 128 x 128 tile = two boxes (head-dim halves), 16 KiB each, both on the same barrier.
+// A whole kRows x 128 tile = two boxes (head-dim halves) of kRows x 128 bytes each, both on the same barrier.
+template <int kRows>
 __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar, int bshd, int row0,
                                               int h, int b) {
   tma_load_tile_half(dst, tm, bar, bshd, 0, row0, h, b);
-  tma_load_tile_half(dst + kTileBytes / 2, tm, bar, bshd, 64, row0, h, b);
+  tma_load_tile_half(dst + kRows * 128, tm, bar, bshd, 64, row0, h, b);
 }
 
 // ---------------------------------------------------------------------------
@@ -246,14 +248,16 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const CUtensorMap* t
 //   low word : [0,14) start address >> 4, [16,30) leading byte offset >> 4
 //   high word: [0,14) stride byte offset >> 4, [14,16) version = 1, [29,32) swizzle = 2 (128 bytes)
 // ---------------------------------------------------------------------------
-constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);                 // SBO = 1024 bytes
-constexpr uint32_t kDescLoKMajor = (16u >> 4) << 16;                                 // LBO unused (1)
-constexpr uint32_t kDescLoMnMajor = (static_cast<uint32_t>(kTileBytes / 2) >> 4) << 16;  // LBO = 16 KiB: next 64 columns
+constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO = 1024 bytes (8 rows of 128 bytes)
+constexpr uint32_t kDescLoKMajor = (16u >> 4) << 16;                  // LBO unused (1)
 
 // Low descriptor word of a tile at shared address `smem` read as a K-major operand (Q, K) ...
 __device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t smem) { return ((smem & 0x3FFFFu) >> 4) | kDescLoKMajor; }
-// ... or as an MN-major operand (V: head dimension contiguous).
-__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem) { return ((smem & 0x3FFFFu) >> 4) | kDescLoMnMajor; }
+// ... or as an MN-major operand (V: head dimension contiguous); LBO = distance of the second 64-column half.
+template <int kRows>
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t smem) {
+  return ((smem & 0x3FFFFu) >> 4) | ((static_cast<uint32_t>(kRows * 128) >> 4) << 16);
+}
 
 __device__ __forceinline__ uint64_t make_desc(uint32_t lo) {
   uint64_t d;
@@ -261,22 +265,25 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t lo) {
   return d;
 }
 
-// S[128 x 128] = Q_tile * K_tile^T, both K-major: 8 MMAs of K = 16 over the head dimension.
-// k-step ks lives in 64-column half (ks >> 2), 32 bytes per step inside the 128-byte swizzle row.
+// S[128 x kKeys] = Q_tile * K_tile^T, both K-major: 8 MMAs of K = 16 over the head dimension.
+// k-step ks lives in 64-column half (ks >> 2) of each tile, 32 bytes per step inside the 128-byte swizzle row.
+template <int kKeys>
 __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_t k_lo) {
-  constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 0, kTileM, kTileN);
+  constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 0, kTileM, kKeys);
 #pragma unroll
   for (int ks = 0; ks < 8; ++ks) {
-    const uint32_t off = ((ks >> 2) * (kTileBytes / 2) + (ks & 3) * 32) >> 4;
-    sm100::umma_ss(d_tmem, make_desc(q_lo + off), make_desc(k_lo + off), idesc, ks > 0 ? 1u : 0u);
+    const uint32_t q_off = ((ks >> 2) * (kTileM * 128) + (ks & 3) * 32) >> 4;
+    const uint32_t k_off = ((ks >> 2) * (kKeys * 128) + (ks & 3) * 32) >> 4;
+    sm100::umma_ss(d_tmem, make_desc(q_lo + q_off), make_desc(k_lo + k_off), idesc, ks > 0 ? 1u : 0u);
   }
 }
-// O[128 x 128] (+)= P (TMEM, bf16 pairs, 8 columns per step) * V_tile (MN-major): 8 MMAs of K = 16 keys,
+// O[128 x 128] (+)= P (TMEM, bf16 pairs, 8 columns per step) * V_tile (MN-major): kKeys / 16 MMAs of K = 16 keys,
 // 16 key rows = 2048 bytes per step.
+template <int kKeys>
 __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo, bool accumulate) {
   constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 1, kTileM, kHeadDim);
 #pragma unroll
-  for (int ks = 0; ks < 8; ++ks) {
+  for (int ks = 0; ks < kKeys / 16; ++ks) {
     sm100::umma_ts(d_tmem, p_tmem + ks * 8, make_desc(v_lo + ks * (2048 >> 4)), idesc,
                    (accumulate || ks > 0) ? 1u : 0u);
   }

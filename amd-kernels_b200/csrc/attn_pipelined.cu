@@ -115,7 +115,7 @@ __device__ __forceinline__ void role_producer(const AttnParams& p, uint32_t base
     const int q_row0 = un.qb * kTaskRows;
     if (it > 0) MA_WAIT(bars + 8 * kBarQEmpty, (it - 1) & 1, 0x10);
     mbar_arrive_expect_tx(bars + 8 * (kBarQFull + 0), kTileBytes);
-    tma_load_tile(base + kOffQ, &p.tm_q, bars + 8 * (kBarQFull + 0), p.bshd, q_row0, un.h, un.b);
+    tma_load_tile<kTileM>(base + kOffQ, &p.tm_q, bars + 8 * (kBarQFull + 0), p.bshd, q_row0, un.h, un.b);
     for (int kb = un.kb_begin; kb < un.kb_end; ++kb) {
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {
@@ -123,12 +123,12 @@ __device__ __forceinline__ void role_producer(const AttnParams& p, uint32_t base
         if (use > 0) MA_WAIT(bars + 8 * (kBarKvEmpty + stage), (use - 1) & 1, 0x11 + kv);
         const uint32_t full = bars + 8 * (kBarKvFull + stage);
         mbar_arrive_expect_tx(full, kTileBytes);
-        tma_load_tile(base + kOffKV + stage * kTileBytes, kv == 0 ? &p.tm_k : &p.tm_v, full, p.bshd, kb * kTileN, un.h,
+        tma_load_tile<kTileN>(base + kOffKV + stage * kTileBytes, kv == 0 ? &p.tm_k : &p.tm_v, full, p.bshd, kb * kTileN, un.h,
                       un.b);
         ++fill;
         if (kv == 0 && kb == un.kb_begin) {  // second Q tile right behind the first K block
           mbar_arrive_expect_tx(bars + 8 * (kBarQFull + 1), kTileBytes);
-          tma_load_tile(base + kOffQ + kTileBytes, &p.tm_q, bars + 8 * (kBarQFull + 1), p.bshd, q_row0 + kTileM, un.h,
+          tma_load_tile<kTileM>(base + kOffQ + kTileBytes, &p.tm_q, bars + 8 * (kBarQFull + 1), p.bshd, q_row0 + kTileM, un.h,
                         un.b);
         }
       }
@@ -143,7 +143,7 @@ __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uin
   const uint32_t bars = base + kOffBars;
   const uint32_t q_lo = desc_lo_kmajor(base + kOffQ);      // + tile  * (kTileBytes >> 4)
   const uint32_t kv_lo_k = desc_lo_kmajor(base + kOffKV);  // + stage * (kTileBytes >> 4)
-  const uint32_t kv_lo_v = desc_lo_mnmajor(base + kOffKV);
+  const uint32_t kv_lo_v = desc_lo_mnmajor<kTileN>(base + kOffKV);
   constexpr uint32_t kTileLo = kTileBytes >> 4;
   uint32_t fill = 0;   // K/V ring fills consumed before this unit
   uint32_t it = 0;     // units so far
@@ -161,7 +161,7 @@ __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uin
       for (uint32_t t = 0; t < 2; ++t) {
         MA_WAIT(bars + 8 * (kBarQFull + t), it & 1, 0x20 + t);
         tc_fence_after_sync();
-        issue_qk(tmem + t * 128, q_lo + t * kTileLo, k_lo);
+        issue_qk<kTileN>(tmem + t * 128, q_lo + t * kTileLo, k_lo);
         umma_commit(bars + 8 * (kBarSFull + t));
       }
       umma_commit(bars + 8 * (kBarKvEmpty + st));
@@ -188,10 +188,10 @@ __device__ __forceinline__ void role_mma(const AttnParams& p, uint32_t base, uin
         MA_WAIT(bars + 8 * (kBarPFull + t), blk & 1, 0x24);
         MA_TRACE_AT(tslot + 2 + 2 * t, tr);
         tc_fence_after_sync();
-        issue_pv(tmem + 256 + t * 128, tmem + t * 128, v_lo, j > 0);
+        issue_pv<kTileN>(tmem + 256 + t * 128, tmem + t * 128, v_lo, j > 0);
         if (t == 1) umma_commit(bars + 8 * (kBarKvEmpty + sv));
         if (more) {
-          issue_qk(tmem + t * 128, q_lo + t * kTileLo, k_lo);
+          issue_qk<kTileN>(tmem + t * 128, q_lo + t * kTileLo, k_lo);
           umma_commit(bars + 8 * (kBarSFull + t));
         } else {
           umma_commit(bars + 8 * (kBarOFull + t));

@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
 
   if (tid == 0) {
     mbar_arrive_expect_tx(bar_q, kTileBytes);
-    tma_load_tile(sQ, &p.tm_q, bar_q, p.bshd, row0, h, b);
+    tma_load_tile<kTileM>(sQ, &p.tm_q, bar_q, p.bshd, row0, h, b);
   }
 
   float m_run = -INFINITY, l_run = 0.f;
@@ -62,8 +62,8 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
   for (int j = 0; j < p.nkb && ok; ++j) {
     if (tid == 0) {
       mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-      tma_load_tile(sK, &p.tm_k, bar_kv, p.bshd, j * kTileN, h, b);
-      tma_load_tile(sV, &p.tm_v, bar_kv, p.bshd, j * kTileN, h, b);
+      tma_load_tile<kTileN>(sK, &p.tm_k, bar_kv, p.bshd, j * kTileN, h, b);
+      tma_load_tile<kTileN>(sV, &p.tm_v, bar_kv, p.bshd, j * kTileN, h, b);
     }
     if (j == 0) ok = mbar_wait_warp(bar_q, 0, 1, ctx);
     ok = ok && mbar_wait_warp(bar_kv, j & 1, 2, ctx);
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
     if (!ok) break;
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_qk(tS, desc_lo_kmajor(sQ), desc_lo_kmajor(sK));
+      issue_qk<kTileN>(tS, desc_lo_kmajor(sQ), desc_lo_kmajor(sK));
       umma_commit(bar_mma);
     }
     ok = mbar_wait_warp(bar_mma, mma_phase, 3, ctx);
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(kSimpleThreads, 1) attn_simple_kernel(const __
 
     if (tid == 0) {
       tc_fence_after_sync();
-      issue_pv(tO, tS, desc_lo_mnmajor(sV), j > 0);
+      issue_pv<kTileN>(tO, tS, desc_lo_mnmajor<kTileN>(sV), j > 0);
       umma_commit(bar_mma);
     }
     ok = mbar_wait_warp(bar_mma, mma_phase, 4, ctx);

@@ -29,7 +29,7 @@ EncodeTiledFn encode_tiled_fn() {
 // Rank-4 map over a contiguous bf16 tensor, rows of 128 head-dim elements.
 // The sequence axis is a dimension of its own, so a box that runs past the end
 // of a sequence reads zeros instead of the next head or batch.
-int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int seq, int bshd) {
+int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int seq, int bshd, int box_rows) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return MA_ERR_DRIVER;
   const cuuint64_t row = ma::kHeadDim * 2;  // bytes
@@ -38,11 +38,11 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int 
   if (bshd) {  // [B, S, H, D]
     dims[0] = ma::kHeadDim, dims[1] = heads, dims[2] = seq, dims[3] = batch;
     strides[0] = row, strides[1] = row * heads, strides[2] = row * heads * seq;
-    box[0] = 64, box[1] = 1, box[2] = ma::kTileN, box[3] = 1;
+    box[0] = 64, box[1] = 1, box[2] = box_rows, box[3] = 1;
   } else {  // [B, H, S, D]
     dims[0] = ma::kHeadDim, dims[1] = seq, dims[2] = heads, dims[3] = batch;
     strides[0] = row, strides[1] = row * seq, strides[2] = row * seq * heads;
-    box[0] = 64, box[1] = ma::kTileN, box[2] = 1, box[3] = 1;
+    box[0] = 64, box[1] = box_rows, box[2] = 1, box[3] = 1;
   }
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
@@ -146,8 +146,7 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
   if (e != cudaSuccess) return cuda_rc(e);
   if (major != 10) return MA_ERR_DEVICE;
 
-  const bool simple = (flags & MA_FLAG_SIMPLE) != 0;
-  const bool want_split = workspace != nullptr && !(flags & MA_FLAG_NO_TAIL) && !simple;
+  const bool want_split = workspace != nullptr && !(flags & (MA_FLAG_NO_TAIL | MA_FLAG_SIMPLE));
   const ma::TailPlan plan = ma::plan_tail(batch, heads, seq_len, seq_len_kv, sms, want_split);
   if (plan.total_units <= 0 || plan.grid <= 0) return MA_ERR_PLAN;
   if (workspace != nullptr) {
@@ -157,9 +156,11 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
 
   ma::AttnParams p;
   std::memset(&p, 0, sizeof(p));
-  rc = make_tensor_map(&p.tm_q, q, batch, heads, seq_len, layout);
-  if (rc == MA_OK) rc = make_tensor_map(&p.tm_k, k, batch, heads, seq_len_kv, layout);
-  if (rc == MA_OK) rc = make_tensor_map(&p.tm_v, v, batch, heads, seq_len_kv, layout);
+  const bool simple = (flags & MA_FLAG_SIMPLE) != 0;
+  const int kv_rows = ma::kTileN;
+  rc = make_tensor_map(&p.tm_q, q, batch, heads, seq_len, layout, ma::kTileM);
+  if (rc == MA_OK) rc = make_tensor_map(&p.tm_k, k, batch, heads, seq_len_kv, layout, kv_rows);
+  if (rc == MA_OK) rc = make_tensor_map(&p.tm_v, v, batch, heads, seq_len_kv, layout, kv_rows);
   if (rc != MA_OK) return rc;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.status = static_cast<uint32_t*>(workspace);
@@ -183,7 +184,7 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
     if (e != cudaSuccess) return cuda_rc(e);
   }
   if (simple) return cuda_rc(ma::launch_attn_simple(p, stream));
-  const int poly = (flags & 0x800) ? ((flags >> 8) & 7) : 2;  // bits 8-11: tuning override
+  const int poly = (flags & 0x800) ? ((flags >> 8) & 7) : 0;  // bits 8-11: tuning override
   e = ma::launch_attn_pipelined(p, plan.grid, poly, stream);
   if (e == cudaSuccess && plan.tail_tasks > 0) e = ma::launch_merge_parts(p, stream);
   return cuda_rc(e);
