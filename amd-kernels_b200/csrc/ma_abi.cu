@@ -3,6 +3,7 @@
 // calls apart from the lazily resolved driver entry point.
 #include <cmath>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/moonmath_attention.h"
 #include "attn_common.cuh"
@@ -64,6 +65,32 @@ int check_dims(int batch, int heads, int seq_len, int seq_len_kv) {
   return MA_OK;
 }
 
+// Scratch of ma_attention_forward_static: lives in the library image, so no call ever allocates it.
+// Every device that loads the library holds one copy until the process exits.
+constexpr size_t kStaticScratchBytes = MA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_addr[kMaxDevices] = {};  // device address of g_static_scratch, per device ordinal
+
+// In host code `g_static_scratch` is only a handle for the runtime, not a device address; the
+// address a kernel can use comes from cudaGetSymbolAddress, asked once per device with that
+// device current.
+int static_scratch_address(int dev, void** out) {
+  if (dev < 0 || dev >= kMaxDevices) return MA_ERR_DEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess) return cuda_rc(e);
+    if (ptr == nullptr || (reinterpret_cast<uintptr_t>(ptr) & 255u)) return MA_ERR_WORKSPACE;
+    g_static_addr[dev] = ptr;
+  }
+  *out = g_static_addr[dev];
+  return MA_OK;
+}
+
 int resolve_sms(int num_sms) {
   if (num_sms > 0) return num_sms;
   return ma_device_sms();
@@ -92,6 +119,9 @@ const char* ma_error_string(int rc) {
     case MA_ERR_DRIVER: return "cuTensorMapEncodeTiled not found in the driver";
     case MA_ERR_DEVICE: return "current CUDA device is not an sm_100 GPU";
     case MA_ERR_TOO_LARGE: return "problem exceeds the kernel's index range";
+    case MA_ERR_STATIC_SCRATCH:
+      return "problem needs more scratch than the built-in static buffer holds (pass MA_FLAG_NO_TAIL or use "
+             "ma_attention_forward with a workspace)";
     default: return rc >= MA_ERR_CUDA_BASE ? "CUDA runtime error (code - 1000 is the cudaError_t)" : "unknown error";
   }
 }
@@ -187,6 +217,43 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
   const int poly = (flags & 0x800) ? ((flags >> 8) & 7) : 0;  // bits 8-11: tuning override
   e = ma::launch_attn_pipelined(p, plan.grid, poly, stream);
   if (e == cudaSuccess && plan.tail_tasks > 0) e = ma::launch_merge_parts(p, stream);
+  return cuda_rc(e);
+}
+
+int ma_attention_forward_static(const void* q, const void* k, const void* v, void* out, int batch, int heads,
+                                int seq_len, int seq_len_kv, int head_dim, int layout, int round_mode, int flags,
+                                void* stream) {
+  const int rc = check_dims(batch, heads, seq_len, seq_len_kv);
+  if (rc != MA_OK) return rc;
+  int dev = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  // Reject before anything is launched: the scratch this problem's plan wants must fit the static buffer.
+  const bool split = !(flags & (MA_FLAG_NO_TAIL | MA_FLAG_SIMPLE));
+  const size_t need = ma::plan_workspace_bytes(ma::plan_tail(batch, heads, seq_len, seq_len_kv, sms, split));
+  if (need > kStaticScratchBytes) return MA_ERR_STATIC_SCRATCH;
+  void* scratch = nullptr;
+  const int arc = static_scratch_address(dev, &scratch);  // first call on a device: symbol lookup
+  if (arc != MA_OK) return arc;
+  // Same kernels and plan as ma_attention_forward, with the static buffer as its workspace.  That
+  // call clears the status block; the partial results are fully rewritten before the merge reads them.
+  return ma_attention_forward(q, k, v, out, batch, heads, seq_len, seq_len_kv, head_dim, layout, round_mode, scratch,
+                              kStaticScratchBytes, flags, stream);
+}
+
+int ma_static_status(uint32_t* host_words, int n, void* stream_) {
+  if (host_words == nullptr) return MA_ERR_NULL_POINTER;
+  if (n < 0 || n > ma::kStatusWords) return MA_ERR_TOO_LARGE;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  void* scratch = nullptr;
+  const int arc = static_scratch_address(dev, &scratch);
+  if (arc != MA_OK) return arc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  e = cudaMemcpyAsync(host_words, scratch, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   return cuda_rc(e);
 }
 

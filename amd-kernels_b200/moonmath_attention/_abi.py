@@ -23,6 +23,8 @@ FLAG_NO_TAIL = 0x1
 FLAG_SIMPLE = 0x2
 FLAG_EXACT_MAX = 0x8
 
+STATIC_SCRATCH_BYTES = 40 << 20  # MA_STATIC_SCRATCH_BYTES
+ERR_STATIC_SCRATCH = 16
 ERR_WAIT_TIMEOUT = 0x57A17  # device status word 0 when a bounded wait gave up
 
 # every symbol include/moonmath_attention.h declares
@@ -33,6 +35,8 @@ EXPORTS = (
     "ma_workspace_bytes",
     "ma_plan_tail",
     "ma_attention_forward",
+    "ma_attention_forward_static",
+    "ma_static_status",
     "ma_round_bf16",
 )
 
@@ -60,6 +64,10 @@ def _load() -> ctypes.CDLL:
     lib.ma_attention_forward.argtypes = (
         [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_size_t, c_int, c_void_p]
     )
+    lib.ma_attention_forward_static.restype = c_int
+    lib.ma_attention_forward_static.argtypes = [c_void_p] * 4 + [c_int] * 8 + [c_void_p]
+    lib.ma_static_status.restype = c_int
+    lib.ma_static_status.argtypes = [c_void_p, c_int, c_void_p]
     lib.ma_round_bf16.restype = c_int
     lib.ma_round_bf16.argtypes = [c_void_p, c_void_p, c_size_t, c_int, c_void_p]
     if lib.ma_abi_version() != ABI_VERSION:

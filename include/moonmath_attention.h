@@ -69,6 +69,7 @@ extern "C" {
 #define MA_ERR_DRIVER 13         /* driver entry point not found */
 #define MA_ERR_DEVICE 14         /* current device is not sm_100 */
 #define MA_ERR_TOO_LARGE 15      /* a dimension exceeds what the kernel indexes */
+#define MA_ERR_STATIC_SCRATCH 16 /* ma_attention_forward_static: the plan needs more than MA_STATIC_SCRATCH_BYTES */
 #define MA_ERR_CUDA_BASE 1000    /* 1000 + cudaError_t of a failed runtime call or launch */
 
 /* Value of MA_ABI_VERSION the library was built with. */
@@ -116,6 +117,39 @@ int ma_plan_tail(int batch, int heads, int seq_len, int seq_len_kv, int num_sms,
 int ma_attention_forward(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
                          int seq_len_kv, int head_dim, int layout, int round_mode, void* workspace,
                          size_t workspace_bytes, int flags, void* stream);
+
+/*
+ * The same operation as ma_attention_forward for callers that must not allocate device memory
+ * and have nowhere to keep a workspace: code running inside another framework's memory pool or
+ * under a fixed memory budget, plug-ins handed only the input and output buffers, and anything
+ * that runs where cudaMalloc is forbidden or would synchronise the device.  (No counterpart in
+ * the reference, whose binding allocates its 121 MB workspace on every call.)
+ *
+ * The scratch (status block + KV-split partial results) is a static device array inside the
+ * library, MA_STATIC_SCRATCH_BYTES large; every GPU that loads the library carries it until the
+ * process exits.  The call performs no cudaMalloc / cudaFree and calls no allocating library
+ * routine.  Limits and rules:
+ *   - a problem whose tail plan wants more scratch than that returns MA_ERR_STATIC_SCRATCH and
+ *     launches nothing; with MA_FLAG_NO_TAIL every problem fits (256 bytes are used);
+ *   - the first call on each device looks up the array's device address (a host-side set-up step);
+ *     make that first call before any stream capture begins;
+ *   - all calls on one device share the one array: calls whose kernels can overlap on the GPU
+ *     (different streams, no ordering between them) race on it and must be serialised by the
+ *     caller.  Calls ordered on one stream are safe; the array keeps the previous call's contents
+ *     and this call rewrites everything it reads (the status block is cleared first).
+ * After the stream has drained, ma_static_status() tells whether the kernels reported a fault.
+ */
+#define MA_STATIC_SCRATCH_BYTES (40u << 20)
+int ma_attention_forward_static(const void* q, const void* k, const void* v, void* out, int batch, int heads,
+                                int seq_len, int seq_len_kv, int head_dim, int layout, int round_mode, int flags,
+                                void* stream);
+
+/*
+ * Copies the first `n` (<= 64) device status words of the static scratch of the current device to
+ * `host_words` (synchronises `stream`).  Word 0 is 0 when the last ma_attention_forward_static on
+ * this device ran clean.  No counterpart in the reference.
+ */
+int ma_static_status(uint32_t* host_words, int n, void* stream);
 
 /*
  * dst[i] = bf16 bits of src[i] under round_mode, NaN -> 0x7FFF; device pointers.
