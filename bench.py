@@ -41,8 +41,8 @@ WORKLOADS = {
 # Reference's published MI300X figures for (2,24,8192,128): README.md:98-100 -> 4*B*H*S^2*D / t.
 PUBLISHED_TFLOPS = {"rtne": 535.0, "rtna": 545.8, "rtz": 552.9}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_pipelined_kernel launch at the c2 shape
-# (profiles/ncu_attn_pipelined_c2.md); None until a capture exists.
-NCU_TRAFFIC_BYTES = {"c2": None}
+# (profiles/ncu_attn_pipelined_c2.md).
+NCU_TRAFFIC_BYTES = {"c2": 302455040 + 87395072}
 
 
 def measured_peaks() -> tuple[float, float, str]:
