@@ -216,19 +216,6 @@ __device__ __forceinline__ void load_scores(uint32_t tS, uint32_t (&s)[128], int
       if (i >= valid) s[i] = __float_as_uint(-INFINITY);
   }
 }
-// Row maximum that is NaN when any score is NaN (and +inf / -inf when the row holds them): one
-// instruction per two scores, and the result tells whether the row needs the exact slow path.
-__device__ __forceinline__ float row_max_nan(const uint32_t (&s)[128]) {
-  float mx[8];
-#pragma unroll
-  for (int c = 0; c < 8; ++c) mx[c] = fmax3_nan(__uint_as_float(s[16 * c]), __uint_as_float(s[16 * c + 1]), -INFINITY);
-#pragma unroll
-  for (int i = 1; i < 8; ++i)
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      mx[c] = fmax3_nan(mx[c], __uint_as_float(s[16 * c + 2 * i]), __uint_as_float(s[16 * c + 2 * i + 1]));
-  return fmax3_nan(fmax3_nan(mx[0], mx[1], mx[2]), fmax3_nan(mx[3], mx[4], mx[5]), fmax3_nan(mx[6], mx[7], mx[7]));
-}
 // Row maximum that ignores NaN scores (fmaxf semantics), for the slow path.
 __device__ __forceinline__ float row_max(const uint32_t (&s)[128]) {
   float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
@@ -240,6 +227,22 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[128]) {
     mx3 = fmaxf(mx3, __uint_as_float(s[96 + i]));
   }
   return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+}
+
+// How far (log2 units) a block's row maximum may exceed the reference maximum before the speculative
+// pass is abandoned: p <= 2^40 and its sums stay far inside fp32 and bf16 range.
+constexpr float kTauHard = 40.f;
+
+// O_row *= alpha for this thread's accumulator row (128 fp32 columns in tensor memory).
+__device__ __forceinline__ void rescale_accumulator(uint32_t tO, float alpha) {
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    uint32_t o[32];
+    tmem_ld32_sync(tO + c * 32, o);
+#pragma unroll
+    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+    tmem_st32(tO + c * 32, o);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -259,7 +262,7 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
   for (int u = blockIdx.x; u < p.total_units; u += gridDim.x, ++it) {
     const Unit un = decode_unit(p, u);
     const int n = un.kb_end - un.kb_begin;
-    float m_ref = 0.f, l_run = 0.f;
+    float m_ref = 0.f, m_seen = 0.f, l_run = 0.f;
     for (int j = 0; j < n; ++j, ++blk) {
       const bool tr = (row == 0) && it == 0 && j < 40;
       const int tslot = tile * 1000 + j * 8;
@@ -270,94 +273,93 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
       uint32_t s[128];
       const int valid = p.seq_kv - (un.kb_begin + j) * kTileN;
       load_scores(tS, s, valid);
-      // Fast path: every score of every row of this warp is finite or -inf (masked / excluded keys).
-      // Otherwise (a NaN or +inf score somewhere, or a row of -inf only) the whole warp takes the
-      // slow path, whose arithmetic propagates NaN and infinities exactly as IEEE arithmetic does.
       MA_TRACE_AT(tslot + 2, tr);
-      float m_blk = row_max_nan(s) * scale;
-      const bool slow = __any_sync(0xffffffffu, !(fabsf(m_blk) < INFINITY));
-      if (slow) m_blk = row_max(s) * scale;
+      uint32_t pk[64];  // P of this block as bf16 pairs; written to tensor memory once the block is known to be safe
 
-      if (j == 0) {
-        // First block of the unit: the accumulator is overwritten, nothing to rescale.
-        m_ref = (m_blk == -INFINITY) ? 0.f : m_blk;
-      } else {
-        // Lazy rescale: move the reference maximum only when it would rise by more than tau.
-        const bool need = (m_blk - m_ref) > p.rescale_tau;
+      // Speculative pass (every block but the first of a unit): exponentiate against the reference
+      // maximum as it stands and find the block's row maximum in the same sweep, so that the maximum
+      // is off the critical path.  The result of softmax does not depend on the reference, only
+      // overflow does: if some row's maximum is NaN / +-inf or exceeds the reference by more than
+      // kTauHard, nothing has been stored yet and the block is redone on the exact path.
+      bool exact = (j == 0) || p.rescale_tau == 0.f;
+      if (!exact) {
+        // Lazy rescale, one block late: move the reference when the maximum seen so far exceeds it by
+        // more than tau.  The accumulator is stable here: S(j) complete implies P V (j-1) complete.
+        const bool need = (m_seen - m_ref) > p.rescale_tau;
         if (__any_sync(0xffffffffu, need)) {
-          const float m_new = fmaxf(m_ref, m_blk);
+          const float m_new = fmaxf(m_ref, m_seen);
           const float alpha = ex2_approx(m_ref - m_new);
           m_ref = m_new;
           l_run *= alpha;
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld32_sync(tO + c * 32, o);
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(tO + c * 32, o);
-          }
-          // The scores were dropped to make room for the accumulator row; fetch them again.
-          load_scores(tS, s, valid);
+          rescale_accumulator(tO, alpha);
         }
-      }
-
-      MA_TRACE_AT(tslot + 3, tr);
-      // p = 2^(s * scale - m_ref); the row sum uses the unrounded values.  P goes out in four chunks of
-      // 32 keys (16 packed registers each) over the first 64 columns of S, whose scores are all in
-      // registers by now.
-      if (!slow) {
+        MA_TRACE_AT(tslot + 3, tr);
         const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int e = 32 * c + 2 * i;
-            float p0, p1;
-            if (kPolyOf4 == 5) {  // experiment: no packed arithmetic at all
-              p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale, -m_ref));
-              p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale, -m_ref));
-              sum[(2 * i) & 3] += p0;
-              sum[(2 * i + 1) & 3] += p1;
-              pk[i] = pack_p(p0, p1);
-              continue;
-            }
-            const f32x2 x = fma2(pack2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), scale2, negm2);
-            if ((i & 3) < kPolyOf4) {
-              ex2_poly2(x, p0, p1);  // FMA pipe
-            } else {
-              float x0, x1;
-              unpack2(x, x0, x1);
-              p0 = ex2_approx(x0);  // special-function unit
-              p1 = ex2_approx(x1);
-            }
-            sum[(2 * i) & 3] += p0;
-            sum[(2 * i + 1) & 3] += p1;
-            pk[i] = pack_p(p0, p1);
+        for (int i = 0; i < 64; ++i) {
+          const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
+          const f32x2 x = fma2(pack2(s0, s1), scale2, negm2);
+          mx[i & 3] = fmax3_nan(mx[i & 3], s0, s1);
+          float p0, p1;
+          if ((i & 3) < kPolyOf4) {
+            ex2_poly2(x, p0, p1);  // FMA pipe
+          } else {
+            float x0, x1;
+            unpack2(x, x0, x1);
+            p0 = ex2_approx(x0);  // special-function unit
+            p1 = ex2_approx(x1);
           }
-          tmem_st16(tS + c * 16, pk);
+          sum[(2 * i) & 3] += p0;
+          sum[(2 * i + 1) & 3] += p1;
+          pk[i] = pack_p(p0, p1);
         }
-        l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-      } else {
+        const float m_blk = fmax3_nan(fmax3_nan(mx[0], mx[1], mx[2]), mx[3], mx[3]) * scale;
+        const bool bad = !(fabsf(m_blk) < INFINITY) || (m_blk - m_ref) > kTauHard;
+        if (__any_sync(0xffffffffu, bad)) {
+          exact = true;
+          load_scores(tS, s, valid);
+        } else {
+          l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+          m_seen = fmaxf(m_seen, m_blk);
+        }
+      }
+      if (exact) {
+        // Exact path: maximum first (NaN scores ignored by the maximum, then propagated by ex2), plain
+        // special-function exponentials: IEEE propagation of NaN and infinities throughout.
+        const float m_blk = row_max(s) * scale;
+        if (j == 0) {
+          // First block of the unit: the accumulator is overwritten, nothing to rescale.
+          m_ref = (m_blk == -INFINITY) ? 0.f : m_blk;
+        } else {
+          const bool need = (m_blk - m_ref) > p.rescale_tau;
+          if (__any_sync(0xffffffffu, need)) {
+            const float m_new = fmaxf(m_ref, m_blk);
+            const float alpha = ex2_approx(m_ref - m_new);
+            m_ref = m_new;
+            l_run *= alpha;
+            rescale_accumulator(tO, alpha);
+            // The scores were dropped to make room for the accumulator row; fetch them again.
+            load_scores(tS, s, valid);
+          }
+        }
+        m_seen = fmaxf(m_ref, m_blk);
+        MA_TRACE_AT(tslot + 3, tr);
         float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int e = 32 * c + 2 * i;
-            const float p0 = ex2_approx(fmaf(__uint_as_float(s[e]), scale, -m_ref));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(s[e + 1]), scale, -m_ref));
-            sum0 += p0;
-            sum1 += p1;
-            pk[i] = pack_p(p0, p1);
-          }
-          tmem_st16(tS + c * 16, pk);
+        for (int i = 0; i < 64; ++i) {
+          const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), scale, -m_ref));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), scale, -m_ref));
+          sum0 += p0;
+          sum1 += p1;
+          pk[i] = pack_p(p0, p1);
         }
         l_run += sum0 + sum1;
       }
+      // P overwrites the first 64 columns of S, whose scores are all in registers (or dead) by now.
+      tmem_st32_at<0>(tS, pk);
+      tmem_st32_at<32>(tS + 32, pk);
       MA_TRACE_AT(tslot + 4, tr);
       tmem_st_wait();
       MA_TRACE_AT(tslot + 5, tr);
@@ -492,7 +494,6 @@ cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, int poly_of_4, 
     case 1: kernel = attn_pipelined_kernel<1>; break;
     case 3: kernel = attn_pipelined_kernel<3>; break;
     case 4: kernel = attn_pipelined_kernel<4>; break;
-    case 5: kernel = attn_pipelined_kernel<5>; break;
     default: break;
   }
   cudaError_t e =

@@ -185,6 +185,25 @@ def test_kv_split_agrees_with_unsplit(ma):
         assert_parity(whole[bh], ref, wabs, "rtne", f"whole bh {bh}")
 
 
+def test_late_dominant_keys_force_the_exact_path(ma):
+    """Scores of the last key block exceed everything before by hundreds of log2 units: the speculative
+    softmax pass must notice (its exponentials would overflow) and redo the block on the exact path;
+    and a slowly growing maximum exercises the deferred lazy rescale."""
+    B, H, Sq, Skv = 1, 3, 384, 1024
+    q, k, v = orc.make_inputs(B, H, Sq, Skv, "bhsd")
+    kf = k.float()
+    kf[:, 0, -128:] *= 40.0                                                          # head 0: late jump
+    kf[:, 1] *= torch.linspace(0.2, 12.0, Skv).view(1, Skv, 1)                       # head 1: steady growth
+    kf[:, 2, 300:428] *= 25.0                                                        # head 2: jump in the middle
+    k = kf.to(torch.bfloat16)
+    for mode in ("rtne", "rtz"):
+        got = gpu_forward(ma, q, k, v, "bhsd", mode)
+        ref = orc.attention_fp32(q, k, v, "bhsd").numpy()
+        wabs = weighted_abs_v(q, k, v, "bhsd").numpy()
+        assert np.isfinite(ref).all()
+        assert_parity(got, ref, wabs, mode, f"late dominant keys {mode}")
+
+
 # ---- NaN / Inf --------------------------------------------------------------------------------------
 @pytest.mark.parametrize("mode", orc.ROUND_MODES)
 def test_special_values_bit_and_position_exact(ma, mode):
