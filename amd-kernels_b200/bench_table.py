@@ -1,0 +1,146 @@
+"""Nine-shape sweep of `moonmath_attention.forward` on B200, laid beside the reference's MI300X table.
+
+Same shapes, input patterns and timing method as the reference's benchmark
+(benchmark/bench_table.py:23-55, benchmark/runner.py:25-76, README.md:87-124):
+BSHD layout, preallocated `out=`, 8 warm-ups, 30 iterations between two CUDA
+events, median of 5 passes; TFLOP/s = 4*B*H*S^2*D / t.  The AITER / Modular MAX
+columns of the reference cannot be reproduced (AMD software); its own published
+milliseconds are printed for comparison.
+
+    python amd-kernels_b200/bench_table.py [--pattern realistic] [--shapes std,long] [--passes 5]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+if HERE not in sys.path:
+    sys.path.insert(0, HERE)
+
+# (label, B, H, S, D) -- benchmark/bench_table.py:23-33
+SHAPES = [
+    ("std", 2, 24, 8192, 128),
+    ("long", 2, 24, 16384, 128),
+    ("wide-long", 1, 32, 16384, 128),
+    ("batch-long", 4, 16, 16384, 128),
+    ("70B", 1, 64, 16384, 128),
+    ("xlong", 2, 24, 32768, 128),
+    ("64k", 2, 16, 65536, 128),
+    ("86k", 2, 8, 86016, 128),
+    ("128k", 1, 16, 131072, 128),
+]
+# The reference's published milliseconds on MI300X (rtne, rtna, rtz), README.md:98-124.
+REFERENCE_MS = {
+    "std": (3.083, 3.022, 2.983), "long": (11.670, 11.479, 11.385), "wide-long": (8.013, 7.828, 7.731),
+    "batch-long": (15.591, 15.331, 15.055), "70B": (15.528, 15.239, 15.040), "xlong": (46.002, 44.440, 44.075),
+    "64k": (117.612, 115.550, 114.665), "86k": (101.071, 100.165, 99.397), "128k": (232.517, 228.475, 226.152),
+}
+MODES = ("rtne", "rtna", "rtz")
+PATTERNS = ("random", "realistic", "ones", "linear", "diag")
+
+
+def make_inputs(B: int, H: int, S: int, D: int, device, pattern: str):
+    """(q, k, v) in (B, S, H, D) bf16; the five patterns of benchmark/runner.py:25-76, seed 42."""
+    g = torch.Generator(device=device)
+    g.manual_seed(42)
+
+    def randn(*shape):
+        return torch.randn(*shape, generator=g, device=device, dtype=torch.float32)
+
+    if pattern == "random":
+        return tuple(randn(B, S, H, D).bfloat16() for _ in range(3))
+    if pattern == "realistic":
+        # Q, V ~ N(0,1); K: uniform direction, norm exp(N(0, 0.6)) * sqrt(D) -- peaked attention rows
+        q = randn(B, S, H, D)
+        k = randn(B, S, H, D)
+        k = k / k.norm(dim=-1, keepdim=True)
+        k = k * (torch.exp(randn(B, S, H, 1) * 0.6) * (D ** 0.5))
+        v = randn(B, S, H, D)
+        return q.bfloat16(), k.bfloat16(), v.bfloat16()
+    if pattern == "ones":
+        return tuple(torch.ones(B, S, H, D, dtype=torch.bfloat16, device=device) for _ in range(3))
+    s_idx = (torch.arange(S, dtype=torch.float32, device=device) / S).view(1, S, 1, 1)
+    d_idx = (torch.arange(D, dtype=torch.float32, device=device) / D).view(1, 1, 1, D)
+    if pattern == "linear":
+        q = (s_idx + 0.1 * d_idx).expand(B, S, H, D).contiguous().bfloat16()
+        k = s_idx.expand(B, S, H, D).contiguous().bfloat16()
+        v = (s_idx + d_idx).expand(B, S, H, D).contiguous().bfloat16()
+        return q, k, v
+    if pattern == "diag":
+        eye = torch.eye(D, dtype=torch.float32, device=device).repeat(S // D + 1, 1)[:S]
+        q = eye.view(1, S, 1, D).expand(B, S, H, D).contiguous().bfloat16()
+        v = s_idx.expand(B, S, H, D).contiguous().bfloat16()
+        return q, q.clone(), v
+    raise ValueError(f"unknown input pattern: {pattern}")
+
+
+def time_passes(fn, warmup: int, iters: int, passes: int) -> float:
+    samples = []
+    for _ in range(passes):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        b.synchronize()
+        samples.append(a.elapsed_time(b) / iters)
+    samples.sort()
+    return samples[len(samples) // 2]
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--pattern", default="realistic", choices=PATTERNS)
+    ap.add_argument("--shapes", default=",".join(s[0] for s in SHAPES))
+    ap.add_argument("--passes", type=int, default=5)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--peak", type=float, default=None, help="bf16 TFLOP/s to report fractions against")
+    ap.add_argument("--json", default=None, help="also write the rows to this file")
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench_table.py needs a CUDA device")
+    import moonmath_attention as ma
+
+    peak = a.peak
+    peaks_file = os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")
+    if peak is None and os.path.exists(peaks_file):
+        peak = float(json.load(open(peaks_file))["bf16_tflops"])
+    dev = torch.device("cuda:0")
+    want = set(a.shapes.split(","))
+    rows = []
+    print(f"| shape (B,H,S,D) | mode | B200 ms | TFLOP/s | % of {peak or '?'} | MI300X ms (reference) | speed-up |")
+    print("|---|---|---|---|---|---|---|")
+    for label, B, H, S, D in SHAPES:
+        if label not in want:
+            continue
+        q, k, v = make_inputs(B, H, S, D, dev, a.pattern)
+        out = torch.empty_like(q)
+        flops = 4.0 * B * H * S * S * D
+        for mi, mode in enumerate(MODES):
+            ms = time_passes(lambda: ma.forward(q, k, v, out=out, round_mode=mode, layout="bshd"),
+                             a.warmup, a.iters, a.passes)
+            status = ma.last_status()[0]
+            tf = flops / ms / 1e9
+            ref_ms = REFERENCE_MS[label][mi]
+            rows.append(dict(label=label, shape=[B, H, S, D], mode=mode, ms=ms, tflops=tf, ref_ms=ref_ms,
+                             status=status, pattern=a.pattern))
+            frac = f"{100 * tf / peak:.1f}" if peak else "-"
+            print(f"| {label} ({B},{H},{S},{D}) | {mode} | {ms:.3f} | {tf:.0f} | {frac} | {ref_ms:.3f} | "
+                  f"{ref_ms / ms:.2f}x |" + ("" if status == 0 else f" status {status:#x}"), flush=True)
+        del q, k, v, out
+        torch.cuda.empty_cache()
+    if a.json:
+        json.dump(rows, open(a.json, "w"), indent=1)
+
+
+if __name__ == "__main__":
+    main()
