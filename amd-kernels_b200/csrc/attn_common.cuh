@@ -71,10 +71,15 @@ __device__ __forceinline__ void record_error(uint32_t* status, uint32_t code, ui
 // Waits for the phase with the given parity of an mbarrier.  Returns false when
 // the wait was abandoned (time limit, or another thread already reported an
 // error); the caller must then unwind to the kernel's common exit.
+// `kSleepNs` > 0 puts the thread to sleep between polls: a polling warp otherwise issues an instruction
+// every few clocks and takes issue slots from the softmax warps that share its scheduler.  Waits whose
+// wake-up latency is on the critical path (MMA issuer) keep kSleepNs = 0.
+template <uint32_t kSleepNs>
 __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
   uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
-    if (sm100::mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (sm100::mbar_try_wait(bar, parity)) return true;
+    if (kSleepNs > 0) asm volatile("nanosleep.u32 %0;" ::"n"(kSleepNs));
     if ((it & 0x3Fu) == 0u) {
       if (*ctx.abort) return false;
       if (ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
@@ -92,13 +97,15 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, ui
     }
   }
 }
+template <uint32_t kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
   if (sm100::mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, site, ctx);
+  return mbar_wait_slow<kSleepNs>(bar, parity, site, ctx);
 }
 // Same, with the verdict made uniform over the warp (needed before warp-collective tcgen05.ld/st).
+template <uint32_t kSleepNs = 0>
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, uint32_t site, const WaitCtx& ctx) {
-  const bool ok = mbar_wait(bar, parity, site, ctx);
+  const bool ok = mbar_wait<kSleepNs>(bar, parity, site, ctx);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -279,13 +286,13 @@ __device__ __forceinline__ void issue_qk(uint32_t d_tmem, uint32_t q_lo, uint32_
 }
 // O[128 x 128] (+)= P (TMEM, bf16 pairs, 8 columns per step) * V_tile (MN-major): kKeys / 16 MMAs of K = 16 keys,
 // 16 key rows = 2048 bytes per step.
-template <int kKeys>
+template <int kKeys, int kFirstStep = 0, int kSteps = kKeys / 16>
 __device__ __forceinline__ void issue_pv(uint32_t d_tmem, uint32_t p_tmem, uint32_t v_lo, bool accumulate) {
   constexpr uint32_t idesc = sm100::umma_idesc(sm100::kFmtBF16, sm100::kFmtBF16, 0, 1, kTileM, kHeadDim);
 #pragma unroll
-  for (int ks = 0; ks < kKeys / 16; ++ks) {
+  for (int ks = kFirstStep; ks < kFirstStep + kSteps; ++ks) {
     sm100::umma_ts(d_tmem, p_tmem + ks * 8, make_desc(v_lo + ks * (2048 >> 4)), idesc,
-                   (accumulate || ks > 0) ? 1u : 0u);
+                   (accumulate || ks > kFirstStep) ? 1u : 0u);
   }
 }
 

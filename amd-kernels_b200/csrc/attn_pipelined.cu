@@ -32,6 +32,10 @@ using namespace sm100;
 constexpr int kThreads = 512;
 constexpr int kStages = 4;  // K/V ring, 32 KiB each
 constexpr uint32_t kTmemCols = 512;
+// Sleep between polls of a barrier that is not complete yet, per role (ns): waiting warps then leave the
+// issue slots (and the power budget) to the working ones.  The MMA issuer spins: its wake-up latency is
+// on the critical path.
+constexpr uint32_t kSleepProducer = 128, kSleepSoftmax = 32, kSleepEpilogue = 1000;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffQ = 0;                                    // 2 tiles
@@ -102,6 +106,10 @@ __device__ unsigned long long g_trace[8192];
   if (!mbar_wait((bar), (parity), (site), ctx)) return
 #define MA_WAIT_WARP(bar, parity, site) \
   if (!mbar_wait_warp((bar), (parity), (site), ctx)) return
+#define MA_WAIT_SLEEP(ns, bar, parity, site) \
+  if (!mbar_wait<ns>((bar), (parity), (site), ctx)) return
+#define MA_WAIT_WARP_SLEEP(ns, bar, parity, site) \
+  if (!mbar_wait_warp<ns>((bar), (parity), (site), ctx)) return
 
 // ---------------------------------------------------------------------------
 // TMA producer (one thread)
@@ -113,14 +121,14 @@ __device__ __forceinline__ void role_producer(const AttnParams& p, uint32_t base
   for (int u = blockIdx.x; u < p.total_units; u += gridDim.x, ++it) {
     const Unit un = decode_unit(p, u);
     const int q_row0 = un.qb * kTaskRows;
-    if (it > 0) MA_WAIT(bars + 8 * kBarQEmpty, (it - 1) & 1, 0x10);
+    if (it > 0) MA_WAIT_SLEEP(kSleepProducer, bars + 8 * kBarQEmpty, (it - 1) & 1, 0x10);
     mbar_arrive_expect_tx(bars + 8 * (kBarQFull + 0), kTileBytes);
     tma_load_tile<kTileM>(base + kOffQ, &p.tm_q, bars + 8 * (kBarQFull + 0), p.bshd, q_row0, un.h, un.b);
     for (int kb = un.kb_begin; kb < un.kb_end; ++kb) {
 #pragma unroll
       for (int kv = 0; kv < 2; ++kv) {
         const uint32_t stage = fill % kStages, use = fill / kStages;
-        if (use > 0) MA_WAIT(bars + 8 * (kBarKvEmpty + stage), (use - 1) & 1, 0x11 + kv);
+        if (use > 0) MA_WAIT_SLEEP(kSleepProducer, bars + 8 * (kBarKvEmpty + stage), (use - 1) & 1, 0x11 + kv);
         const uint32_t full = bars + 8 * (kBarKvFull + stage);
         mbar_arrive_expect_tx(full, kTileBytes);
         tma_load_tile<kTileN>(base + kOffKV + stage * kTileBytes, kv == 0 ? &p.tm_k : &p.tm_v, full, p.bshd, kb * kTileN, un.h,
@@ -267,7 +275,7 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
       const bool tr = (row == 0) && it == 0 && j < 40;
       const int tslot = tile * 1000 + j * 8;
       MA_TRACE_AT(tslot + 0, tr);
-      MA_WAIT_WARP(bar_s, blk & 1, 0x30 + tile);
+      MA_WAIT_WARP_SLEEP(kSleepSoftmax, bar_s, blk & 1, 0x30 + tile);
       MA_TRACE_AT(tslot + 1, tr);
       tc_fence_after_sync();
       uint32_t s[128];
@@ -390,7 +398,7 @@ __device__ __forceinline__ void role_epilogue(const AttnParams& p, uint8_t* smem
     const Unit un = decode_unit(p, u);
 #pragma unroll 1
     for (int tile = 0; tile < 2; ++tile) {
-      MA_WAIT_WARP(bars + 8 * (kBarOFull + tile), it & 1, 0x40 + tile);
+      MA_WAIT_WARP_SLEEP(kSleepEpilogue, bars + 8 * (kBarOFull + tile), it & 1, 0x40 + tile);
       MA_WAIT_WARP(bars + 8 * (kBarLReady + tile), it & 1, 0x42 + tile);
       tc_fence_after_sync();
       const float* st = stats + (((it & 1) * 2 + tile) * 128 + row) * 2;
