@@ -60,7 +60,9 @@ inline TailPlan plan_tail(int batch, int heads, int seq_q, int seq_kv, int num_s
     const long long rounds = (static_cast<long long>(tail) * g + num_sms - 1) / num_sms;
     const long long per_part = (t.nkb + g - 1) / g + kPartOverheadBlocks;
     const long long span = rounds * per_part + kMergeCostBlocks;
-    if (span < best) {
+    // A split must beat the unsplit last round by a margin (10 %): measured on B200, marginal
+    // predictions (e.g. 108 stranded tasks of 32 blocks) lose to the extra partial traffic and merge.
+    if (span < best && span * 11 < t.span_nosplit * 10) {
       best = span;
       best_g = g;
     }

@@ -76,6 +76,8 @@ def test_decisions_at_benchmark_shapes():
     assert ma.plan_tail(2, 24, 8192, 512, SMS)["tail_tasks"] == 0
     # even grids are never split
     assert ma.plan_tail(1, 148, 256, 4096, SMS)["tail_tasks"] == 0
+    # a marginal prediction (108 stranded tasks of 32 blocks; measured slower when split) is left alone
+    assert ma.plan_tail(2, 8, 4096, 4096, SMS)["tail_tasks"] == 0
 
 
 def test_split_never_loses_to_no_split_in_the_model():
@@ -86,4 +88,4 @@ def test_split_never_loses_to_no_split_in_the_model():
             continue
         g, tail, nkb = p["split"], p["tail_tasks"], p["nkb"]
         span = math.ceil(tail * g / SMS) * (math.ceil(nkb / g) + 1) + 4
-        assert span < nkb + 1
+        assert span * 11 < (nkb + 1) * 10  # the 10 % margin of the planner
