@@ -140,6 +140,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float lg2_approx(float x) {
+  float y;
+  asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Three-input maximum; NaN in any operand gives NaN (so a row maximum doubles as a NaN detector).
 __device__ __forceinline__ float fmax3_nan(float a, float b, float c) {
   float d;

@@ -237,9 +237,9 @@ __device__ __forceinline__ float row_max(const uint32_t (&s)[128]) {
   return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 }
 
-// How far (log2 units) a block's row maximum may exceed the reference maximum before the speculative
-// pass is abandoned: p <= 2^40 and its sums stay far inside fp32 and bf16 range.
-constexpr float kTauHard = 40.f;
+// Largest row sum of one block (relative to the reference maximum) the speculative pass accepts:
+// p <= 2^40, so P and the accumulators stay far inside bf16 and fp32 range.
+constexpr float kSumHard = 1.099511627776e12f;  // 2^40
 
 // O_row *= alpha for this thread's accumulator row (128 fp32 columns in tensor memory).
 __device__ __forceinline__ void rescale_accumulator(uint32_t tO, float alpha) {
@@ -285,10 +285,9 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
       uint32_t pk[64];  // P of this block as bf16 pairs; written to tensor memory once the block is known to be safe
 
       // Speculative pass (every block but the first of a unit): exponentiate against the reference
-      // maximum as it stands and find the block's row maximum in the same sweep, so that the maximum
-      // is off the critical path.  The result of softmax does not depend on the reference, only
-      // overflow does: if some row's maximum is NaN / +-inf or exceeds the reference by more than
-      // kTauHard, nothing has been stored yet and the block is redone on the exact path.
+      // maximum as it stands, without looking for the block's maximum first.  The result of softmax
+      // does not depend on the reference, only overflow does: if the block's row sum is NaN, +inf or
+      // above kSumHard, nothing has been stored yet and the block is redone on the exact path.
       bool exact = (j == 0) || p.rescale_tau == 0.f;
       if (!exact) {
         // Lazy rescale, one block late: move the reference when the maximum seen so far exceeds it by
@@ -303,13 +302,10 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
         }
         MA_TRACE_AT(tslot + 3, tr);
         const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          const float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
-          const f32x2 x = fma2(pack2(s0, s1), scale2, negm2);
-          mx[i & 3] = fmax3_nan(mx[i & 3], s0, s1);
+          const f32x2 x = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
           float p0, p1;
           if ((i & 3) < kPolyOf4) {
             ex2_poly2(x, p0, p1);  // FMA pipe
@@ -319,18 +315,24 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
             p0 = ex2_approx(x0);  // special-function unit
             p1 = ex2_approx(x1);
           }
-          sum[(2 * i) & 3] += p0;
-          sum[(2 * i + 1) & 3] += p1;
+          sum2[i & 1] = add2(sum2[i & 1], pack2(p0, p1));
           pk[i] = pack_p(p0, p1);
         }
-        const float m_blk = fmax3_nan(fmax3_nan(mx[0], mx[1], mx[2]), mx[3], mx[3]) * scale;
-        const bool bad = !(fabsf(m_blk) < INFINITY) || (m_blk - m_ref) > kTauHard;
+        float sa, sb, sc, sd;
+        unpack2(sum2[0], sa, sb);
+        unpack2(sum2[1], sc, sd);
+        const float sum_blk = (sa + sb) + (sc + sd);
+        // The block's row sum doubles as overflow guard and as estimate of the block maximum: with 128
+        // keys, max x <= log2(sum) <= max x + 7.  NaN (a NaN score) and +inf (an overflow or a +inf
+        // score) fail the comparison too.  No instruction of the sweep is spent on the maximum: a warp
+        // cannot overlap its own special-function issue with other work, so every one counts.
+        const bool bad = !(sum_blk <= kSumHard);
         if (__any_sync(0xffffffffu, bad)) {
           exact = true;
           load_scores(tS, s, valid);
         } else {
-          l_run += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-          m_seen = fmaxf(m_seen, m_blk);
+          l_run += sum_blk;
+          m_seen = fmaxf(m_seen, m_ref + lg2_approx(sum_blk));
         }
       }
       if (exact) {
