@@ -33,8 +33,8 @@ constexpr int kThreads = 512;
 constexpr int kStages = 4;  // K/V ring, 32 KiB each
 constexpr uint32_t kTmemCols = 512;
 // Sleep between polls of a barrier that is not complete yet, per role (ns): waiting warps then leave the
-// issue slots (and the power budget) to the working ones.  The MMA issuer spins: its wake-up latency is
-// on the critical path.
+// issue slots (and the power budget) to the working ones.  The MMA issuer does not sleep (its wake-up
+// latency is on the critical path); every poll, its own included, carries a suspend-time hint.
 constexpr uint32_t kSleepProducer = 128, kSleepSoftmax = 32, kSleepEpilogue = 1000;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
