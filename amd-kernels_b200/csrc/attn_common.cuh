@@ -51,6 +51,21 @@ struct AttnParams {
   float rescale_tau; // lazy-rescale threshold in log2 units (0 = always track the exact max)
 };
 
+// LiteAttention launch (skip lists: lite_list.h).  `a` carries the tensor maps (K and V with 64-row boxes),
+// output, status block, dimensions, layout, rounding and softmax constants; the tail-split fields are unused.
+struct LiteParams {
+  AttnParams a;
+  const int16_t* read_list;  // [tasks][row_width]
+  int16_t* write_list;       // [tasks][row_width]
+  const int16_t* must_do;    // [len, s0, e0, ...] or null
+  const int* order;          // task of each hand-out slot, heaviest first; null = identity
+  int* counter;              // hand-out counter, zero at launch
+  int num_tasks;             // batch * heads * query blocks
+  int row_width;             // 64-key blocks + 2
+  int phase;                 // 1: blocks walked upwards, 0: downwards
+  float threshold;           // log2 units, negative
+};
+
 // ---------------------------------------------------------------------------
 // bounded waits
 // ---------------------------------------------------------------------------

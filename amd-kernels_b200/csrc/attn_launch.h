@@ -11,6 +11,7 @@
 namespace ma {
 
 struct AttnParams;
+struct LiteParams;
 
 // One CTA per 128-row query tile, fully serialised (cross-check kernel).
 cudaError_t launch_attn_simple(const AttnParams& p, cudaStream_t stream);
@@ -21,6 +22,11 @@ cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, int poly_of_4, 
 
 // Combines the partial results of KV-split tasks into the bf16 output.
 cudaError_t launch_merge_parts(const AttnParams& p, cudaStream_t stream);
+
+// LiteAttention: the skip-list driven kernel, and the kernel that sorts its tasks longest-first into `order`
+// (and zeroes the hand-out counter).
+cudaError_t launch_attn_lite(const LiteParams& p, int grid, cudaStream_t stream);
+cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stream);
 
 // dst[i] = bf16(src[i]) with the given rounding mode (device pointers); exposes the
 // epilogue's rounding code for exhaustive bit-pattern tests.

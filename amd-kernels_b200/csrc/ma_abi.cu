@@ -8,6 +8,7 @@
 #include "../../include/moonmath_attention.h"
 #include "attn_common.cuh"
 #include "attn_launch.h"
+#include "lite_list.h"
 
 namespace {
 
@@ -108,6 +109,7 @@ const char* ma_error_string(int rc) {
     case MA_ERR_BATCH_HEADS: return "batch and heads must be positive";
     case MA_ERR_SEQ_Q: return "seq_len must be positive";
     case MA_ERR_HEAD_DIM: return "head_dim must be 128";
+    case MA_ERR_LISTS: return "read_list and write_list must not be null";
     case MA_ERR_SEQ_KV: return "seq_len_kv must be positive";
     case MA_ERR_PLAN: return "tail plan could not be set up";
     case MA_ERR_LAYOUT: return "layout must be 0 (bhsd) or 1 (bshd)";
@@ -119,6 +121,7 @@ const char* ma_error_string(int rc) {
     case MA_ERR_DRIVER: return "cuTensorMapEncodeTiled not found in the driver";
     case MA_ERR_DEVICE: return "current CUDA device is not an sm_100 GPU";
     case MA_ERR_TOO_LARGE: return "problem exceeds the kernel's index range";
+    case MA_ERR_LITE_ARGS: return "threshold must be negative, phase 0 or 1, at most 32766 key blocks of 64";
     case MA_ERR_STATIC_SCRATCH:
       return "problem needs more scratch than the built-in static buffer holds (pass MA_FLAG_NO_TAIL or use "
              "ma_attention_forward with a workspace)";
@@ -255,6 +258,82 @@ int ma_static_status(uint32_t* host_words, int n, void* stream_) {
   e = cudaMemcpyAsync(host_words, scratch, sizeof(uint32_t) * n, cudaMemcpyDeviceToHost, stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
   return cuda_rc(e);
+}
+
+size_t ma_lite_workspace_bytes(int batch, int heads, int seq_len) {
+  if (batch <= 0 || heads <= 0 || seq_len <= 0) return ma::kStatusBytes + 256;
+  const size_t tasks = static_cast<size_t>(batch) * heads * ((seq_len + ma::kLiteQueryBlock - 1) / ma::kLiteQueryBlock);
+  return ma::kStatusBytes + 256 + ((tasks * sizeof(int) + 255) & ~static_cast<size_t>(255));
+}
+
+void ma_lite_tile(int* query_rows, int* key_rows) {
+  if (query_rows != nullptr) *query_rows = ma::kLiteQueryBlock;
+  if (key_rows != nullptr) *key_rows = ma::kLiteKeyBlock;
+}
+
+int ma_attention_forward_lite(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                              int seq_len_kv, int head_dim, int layout, int round_mode, const void* read_list,
+                              void* write_list, const void* must_do_list, float threshold, int phase, void* workspace,
+                              size_t workspace_bytes, int flags, void* stream_) {
+  int rc = check_dims(batch, heads, seq_len, seq_len_kv);
+  if (rc != MA_OK) return rc;
+  if (head_dim != ma::kHeadDim) return MA_ERR_HEAD_DIM;
+  if (read_list == nullptr || write_list == nullptr) return MA_ERR_LISTS;
+  if (layout != MA_LAYOUT_BHSD && layout != MA_LAYOUT_BSHD) return MA_ERR_LAYOUT;
+  if (round_mode < MA_ROUND_RTNE || round_mode > MA_ROUND_RTZ) return MA_ERR_ROUND_MODE;
+  if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return MA_ERR_NULL_POINTER;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                         reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
+  if (bits & 15u) return MA_ERR_ALIGNMENT;
+  const int key_blocks = (seq_len_kv + ma::kLiteKeyBlock - 1) / ma::kLiteKeyBlock;
+  if (!(threshold < 0.f) || (phase != 0 && phase != 1) || key_blocks > 32766) return MA_ERR_LITE_ARGS;
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
+      workspace_bytes < ma_lite_workspace_bytes(batch, heads, seq_len))
+    return MA_ERR_WORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  int dev = 0, major = 0, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (major != 10) return MA_ERR_DEVICE;
+
+  ma::LiteParams p;
+  std::memset(&p, 0, sizeof(p));
+  rc = make_tensor_map(&p.a.tm_q, q, batch, heads, seq_len, layout, ma::kTileM);
+  if (rc == MA_OK) rc = make_tensor_map(&p.a.tm_k, k, batch, heads, seq_len_kv, layout, ma::kLiteKeyBlock);
+  if (rc == MA_OK) rc = make_tensor_map(&p.a.tm_v, v, batch, heads, seq_len_kv, layout, ma::kLiteKeyBlock);
+  if (rc != MA_OK) return rc;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.a.out = static_cast<__nv_bfloat16*>(out);
+  p.a.status = reinterpret_cast<uint32_t*>(ws);
+  p.a.batch = batch, p.a.heads = heads, p.a.seq_q = seq_len, p.a.seq_kv = seq_len_kv;
+  p.a.bshd = layout, p.a.round_mode = round_mode;
+  p.a.nqb = (seq_len + ma::kLiteQueryBlock - 1) / ma::kLiteQueryBlock;
+  p.a.nkb = key_blocks;
+  p.a.scale_log2e = 1.4426950408889634f / sqrtf(static_cast<float>(ma::kHeadDim));
+  p.a.rescale_tau = 8.f;
+  p.read_list = static_cast<const int16_t*>(read_list);
+  p.write_list = static_cast<int16_t*>(write_list);
+  p.must_do = static_cast<const int16_t*>(must_do_list);
+  p.counter = reinterpret_cast<int*>(ws + ma::kStatusBytes);
+  p.num_tasks = batch * heads * p.a.nqb;
+  p.row_width = key_blocks + 2;
+  p.phase = phase;
+  p.threshold = threshold;
+
+  // status block and hand-out counter
+  e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes + 256, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (!(flags & MA_FLAG_LITE_PLAIN)) {
+    int* order = reinterpret_cast<int*>(ws + ma::kStatusBytes + 256);
+    e = ma::launch_lite_order(p, order, stream);
+    if (e != cudaSuccess) return cuda_rc(e);
+    p.order = order;
+  }
+  const int grid = p.num_tasks < sms ? p.num_tasks : sms;
+  return cuda_rc(ma::launch_attn_lite(p, grid, stream));
 }
 
 int ma_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, void* stream) {

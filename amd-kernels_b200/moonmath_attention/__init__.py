@@ -10,12 +10,14 @@ name (moonmath_attention/__init__.py:11-31, moonmath_attention/_kernel.py:14-82)
 >>> v = torch.randn(1, 4, 1024, 128, dtype=torch.bfloat16, device="cuda")
 >>> out = ma.forward(q, k, v)         # torch.bfloat16, same shape
 
-Only the dense forward is provided.  The package talks to the CUDA kernels
+`forward_lite` / `LiteAttention` (moonmath_attention/lite.py of the reference) skip key blocks between
+denoising steps.  The MLA decode operators of the reference are not provided.  The package talks to the CUDA kernels
 through a ctypes binding of libmoonmath_attention_sm100.so; importing it fails
 if that library has not been built.
 """
 
-from ._kernel import forward, last_status, plan_tail, workspace_bytes
+from ._kernel import forward, forward_lite, last_status, plan_tail, workspace_bytes
+from .lite import LiteAttention
 from . import _abi as abi
 
-__all__ = ["forward", "plan_tail", "workspace_bytes", "last_status", "abi"]
+__all__ = ["forward", "forward_lite", "LiteAttention", "plan_tail", "workspace_bytes", "last_status", "abi"]

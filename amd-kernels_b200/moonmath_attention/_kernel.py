@@ -169,3 +169,112 @@ def forward(
         return _forward_cuda(q, k, v, out, round_mode, layout, _flags)
     else:
         raise NotImplementedError(f"Unsupported device {q.device!r}; expected 'cpu' or 'cuda'")
+
+
+def _check_list(t, name: str, device) -> None:
+    # reference: check_list, csrc/attention_api.cpp:329-339 (std::invalid_argument -> ValueError)
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be torch.Tensor; got {type(t).__name__}")
+    if t.dtype != torch.int16:
+        raise ValueError(f"{name} must be int16, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if t.device != device:
+        raise ValueError(f"{name} must be on the same device as q")
+
+
+def forward_lite(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    read_list: torch.Tensor,
+    write_list: torch.Tensor,
+    *,
+    threshold: float,
+    phase: int,
+    must_do_list: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    round_mode: str = "rtna",
+    layout: str = "bhsd",
+) -> torch.Tensor:
+    """LiteAttention forward: compute only the key blocks the skip list names, write the next list.
+
+    Same signature as the reference's entry (moonmath_attention/_kernel.py:85-134; binding
+    csrc/attention_api.cpp:287-434).  `read_list` / `write_list` are int16 CUDA tensors
+    [B, H, qtiles, ktiles + 2], the two halves of the double buffer `LiteAttention` owns
+    (read = skip[phase before the flip], write = the other; `phase` is the value after the flip).
+    qtiles = ceil(Sq / 256), ktiles = ceil(Skv / 64): `LiteAttention.get_MN()`.  A key block is dropped
+    from the written list when, for every group of 32 query rows of the tile, its largest score lies
+    more than |threshold| (log2 units) below the group's rows' running maxima.
+
+    `must_do_list` (optional): one global int16 1-D tensor [len, start0, end0, start1, end1, ...] of
+    key-block ranges [start, end) that are always written as "compute".
+
+    GPU tensors only.  The output approximates full attention (skipped blocks contribute nothing); with a
+    compute-all list and a threshold no block falls under, it is full attention.
+    """
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        _check_tensor(t, name, layout)
+    if round_mode not in _abi.ROUND_MODE:
+        raise ValueError(f"round_mode must be 'rtna', 'rtne', or 'rtz', got '{round_mode}'")
+    if layout not in _abi.LAYOUT:
+        raise ValueError(f"layout must be 'bhsd' or 'bshd', got '{layout}'")
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if t.device.type != "cuda":
+            raise ValueError(f"{name} must be on a CUDA device (GPU-only), got device={t.device}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+    sax, hax = (1, 2) if layout == "bshd" else (2, 1)
+    B, H, Sq, D = q.size(0), q.size(hax), q.size(sax), q.size(3)
+    Skv = k.size(sax)
+    if D != 128:
+        raise ValueError(f"head_dim must be 128, got {D}")
+    if q.device != k.device or q.device != v.device:
+        raise ValueError("q, k, v must be on the same device")
+    if k.size(0) != B or k.size(hax) != H or k.size(3) != D or tuple(v.shape) != tuple(k.shape):
+        raise ValueError(f"k / v shape mismatch: q.shape={tuple(q.shape)}, k.shape={tuple(k.shape)}, v.shape={tuple(v.shape)}")
+    _check_list(read_list, "read_list", q.device)
+    _check_list(write_list, "write_list", q.device)
+    if must_do_list is not None:
+        _check_list(must_do_list, "must_do_list", q.device)
+    tile_m, tile_n = _abi.lite_tile()
+    need = B * H * ((Sq + tile_m - 1) // tile_m) * ((Skv + tile_n - 1) // tile_n + 2)
+    for name, t in (("read_list", read_list), ("write_list", write_list)):
+        if t.numel() != need:
+            raise ValueError(
+                f"{name} must hold B*H*ceil(Sq/{tile_m})*(ceil(Skv/{tile_n})+2) = {need} int16 values, got {t.numel()}"
+            )
+    if out is not None:
+        _check_tensor(out, "out", layout)
+        if tuple(out.shape) != tuple(q.shape):
+            raise ValueError("out shape must match q.shape")
+        if out.device != q.device:
+            raise ValueError("out must be on the same device as q")
+        if not out.is_contiguous():
+            raise ValueError("out must be contiguous")
+    else:
+        out = torch.empty_like(q)
+
+    flags = _abi.FLAG_LITE_PLAIN if os.environ.get("MOONMATH_LITE_PLAIN") else 0  # csrc/attention_api.cpp:403
+    with torch.cuda.device(q.device):
+        stream = torch.cuda.current_stream(q.device).cuda_stream
+        ws_bytes = int(_abi.lib.ma_lite_workspace_bytes(B, H, Sq))
+        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+        rc = _abi.lib.ma_attention_forward_lite(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+            B, H, Sq, Skv, D, _abi.LAYOUT[layout], _abi.ROUND_MODE[round_mode],
+            read_list.data_ptr(), write_list.data_ptr(),
+            must_do_list.data_ptr() if must_do_list is not None else None,
+            float(threshold), int(phase), workspace.data_ptr(), ws_bytes, flags, stream,
+        )
+    if rc != 0:
+        raise RuntimeError(f"launch_attention_forward_lite returned error code {rc}: {_abi.error_string(rc)}")
+    _LAST["workspace"] = workspace
+    if os.environ.get("MOONMATH_CHECK"):
+        st = last_status()
+        if st[0] != 0:
+            raise RuntimeError(
+                f"moonmath_attention lite kernel reported status {st[0]:#x} (site {st[1] & 0xFF:#x}, "
+                f"cta {st[1] >> 8}, detail {st[2]})"
+            )
+    return out

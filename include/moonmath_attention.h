@@ -52,12 +52,16 @@ extern "C" {
                                     MOONMATH_NO_TAIL, csrc/attention_api.cpp:258-267) */
 #define MA_FLAG_SIMPLE 0x2       /* run the serialised cross-check kernel instead of the pipelined one */
 #define MA_FLAG_EXACT_MAX 0x8    /* rescale the accumulator whenever the running maximum rises (tau = 0) */
+#define MA_FLAG_LITE_PLAIN 0x20  /* ma_attention_forward_lite: hand tasks out in index order, not longest-first
+                                    (reference: MOONMATH_LITE_PLAIN / null workspace, csrc/attention_api.cpp:400-407) */
 
 /* return codes: 1, 2, 3, 5, 6 keep the reference's meaning (csrc/attention_kernel.hip:1573-1576, :1588) */
 #define MA_OK 0
 #define MA_ERR_BATCH_HEADS 1     /* batch <= 0 or heads <= 0 */
 #define MA_ERR_SEQ_Q 2           /* seq_len <= 0 */
 #define MA_ERR_HEAD_DIM 3        /* head_dim != 128 */
+#define MA_ERR_LISTS 4           /* ma_attention_forward_lite: read_list or write_list is null
+                                    (reference: csrc/attention_kernel.hip:1627) */
 #define MA_ERR_SEQ_KV 5          /* seq_len_kv <= 0 */
 #define MA_ERR_PLAN 6            /* the tail plan could not be set up */
 #define MA_ERR_LAYOUT 7
@@ -70,6 +74,7 @@ extern "C" {
 #define MA_ERR_DEVICE 14         /* current device is not sm_100 */
 #define MA_ERR_TOO_LARGE 15      /* a dimension exceeds what the kernel indexes */
 #define MA_ERR_STATIC_SCRATCH 16 /* ma_attention_forward_static: the plan needs more than MA_STATIC_SCRATCH_BYTES */
+#define MA_ERR_LITE_ARGS 17      /* threshold >= 0, phase not 0 / 1, or more than 32766 key blocks of 64 */
 #define MA_ERR_CUDA_BASE 1000    /* 1000 + cudaError_t of a failed runtime call or launch */
 
 /* Value of MA_ABI_VERSION the library was built with. */
@@ -150,6 +155,34 @@ int ma_attention_forward_static(const void* q, const void* k, const void* v, voi
  * this device ran clean.  No counterpart in the reference.
  */
 int ma_static_status(uint32_t* host_words, int n, void* stream);
+
+/*
+ * LiteAttention forward.  Replaces launch_attention_forward_lite_{rtna,rtne,rtz}
+ * (csrc/attention_kernel.hip:1604-1681; bound from csrc/attention_api.cpp:287-434) together with the
+ * V transpose and the allocations of its caller.
+ *
+ * read_list / write_list: int16 device arrays [batch][heads][query blocks][key blocks + 2], one
+ * run-length row per task in the reference's format (csrc/attention_kernel.hip:629-716;
+ * moonmath_attention/lite.py:108-128): [len, markers...], read from the back in the direction `phase`
+ * names (1 upwards, 0 downwards).  Only the key blocks the read row names are loaded and computed; the
+ * row written for the next call keeps the blocks for which some group of query rows found a score
+ * within `threshold` (log2 units, negative) of its running maximum.  The block geometry is this
+ * library's (ma_lite_tile): 256 query rows per list row where the reference has 384
+ * (moonmath_attention/lite.py:36-37), 64 keys per block as in the reference, votes per 32 query rows
+ * where the reference votes per 48; lists are therefore exchanged only between calls of this library.
+ * must_do_list: optional global [len, s0, e0, s1, e1, ...] of key-block ranges [s, e) always written as
+ * "compute" (csrc/attention_kernel.hip:676-701), or null.
+ * workspace: ma_lite_workspace_bytes() bytes, 256-byte aligned, required (status block, hand-out
+ * counter, longest-first order: plan_lite_order, csrc/attention_kernel.hip:1296-1347).
+ * Return codes as ma_attention_forward, plus MA_ERR_LISTS (4, the reference's code) and MA_ERR_LITE_ARGS.
+ */
+size_t ma_lite_workspace_bytes(int batch, int heads, int seq_len);
+/* Query rows per list row and keys per list block (reference: KBLOCK_M, KBLOCK_N, moonmath_attention/lite.py:36-37). */
+void ma_lite_tile(int* query_rows, int* key_rows);
+int ma_attention_forward_lite(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                              int seq_len_kv, int head_dim, int layout, int round_mode, const void* read_list,
+                              void* write_list, const void* must_do_list, float threshold, int phase, void* workspace,
+                              size_t workspace_bytes, int flags, void* stream);
 
 /*
  * dst[i] = bf16 bits of src[i] under round_mode, NaN -> 0x7FFF; device pointers.

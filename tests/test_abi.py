@@ -31,9 +31,9 @@ def test_abi_version_and_error_strings():
     assert _abi.lib.ma_abi_version() == 1
     m = re.search(r"#define MA_ABI_VERSION (\d+)", open(HEADER).read())
     assert int(m.group(1)) == _abi.ABI_VERSION
-    for rc in (0, 1, 2, 3, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 1001):
-        assert _abi.error_string(rc)
-    assert "unknown" in _abi.error_string(4)
+    for rc in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 1001):
+        assert _abi.error_string(rc) and "unknown" not in _abi.error_string(rc)
+    assert "unknown" in _abi.error_string(18)
 
 
 def _call(q=16, k=16, v=16, out=16, B=1, H=1, Sq=128, Skv=128, D=128, layout=0, mode=0, ws=0, wsb=0, flags=0):
@@ -65,3 +65,17 @@ def test_no_gpu_means_an_error_not_a_fallback():
 def test_round_bf16_rejects_bad_arguments():
     assert _abi.lib.ma_round_bf16(0, 0, 0, 5, 0) == 8
     assert _abi.lib.ma_round_bf16(0, 0, 4, 0, 0) == 9
+
+
+def test_lite_argument_validation_return_codes():
+    """ma_attention_forward_lite: codes 1, 2, 3, 4, 5 as the reference's launcher (csrc/attention_kernel.hip:1623-1627)."""
+    def call(B=1, H=1, Sq=128, Skv=128, D=128, layout=0, mode=0, rl=16, wl=16, thr=-3.0, phase=1, ws=0, wsb=0, q=16):
+        return _abi.lib.ma_attention_forward_lite(q, 16, 16, 16, B, H, Sq, Skv, D, layout, mode, rl, wl, None,
+                                                  ctypes.c_float(thr), phase, ws, wsb, 0, None)
+    assert call(B=0) == 1 and call(Sq=0) == 2 and call(D=64) == 3 and call(Skv=0) == 5
+    assert call(rl=None) == 4 and call(wl=None) == 4
+    assert call(layout=3) == 7 and call(mode=5) == 8 and call(q=None) == 9 and call(q=8) == 10
+    assert call(thr=0.0) == 17 and call(phase=-1) == 17 and call(Skv=64 * 40000) == 17
+    assert call() == 11  # workspace is required
+    assert _abi.lib.ma_lite_workspace_bytes(2, 24, 8192) == 256 + 256 + 2 * 24 * 32 * 4
+    assert _abi.lite_tile() == (256, 64)
