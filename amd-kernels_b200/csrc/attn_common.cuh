@@ -170,10 +170,10 @@ __device__ __forceinline__ float lg2_approx(float x) {
   return y;
 }
 
-// Three-input maximum; NaN in any operand gives NaN (so a row maximum doubles as a NaN detector).
-__device__ __forceinline__ float fmax3_nan(float a, float b, float c) {
+// Three-input maximum in one instruction; NaN operands are ignored (fmaxf semantics).
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
-  asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 

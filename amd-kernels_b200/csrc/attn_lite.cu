@@ -231,13 +231,13 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
 __device__ __forceinline__ float half_max(const uint32_t* s) {
   float m0 = -INFINITY, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    m0 = fmaxf(m0, __uint_as_float(s[i]));
-    m1 = fmaxf(m1, __uint_as_float(s[16 + i]));
-    m2 = fmaxf(m2, __uint_as_float(s[32 + i]));
-    m3 = fmaxf(m3, __uint_as_float(s[48 + i]));
+  for (int i = 0; i < 8; ++i) {
+    m0 = fmax3(m0, __uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1]));
+    m1 = fmax3(m1, __uint_as_float(s[16 + 2 * i]), __uint_as_float(s[16 + 2 * i + 1]));
+    m2 = fmax3(m2, __uint_as_float(s[32 + 2 * i]), __uint_as_float(s[32 + 2 * i + 1]));
+    m3 = fmax3(m3, __uint_as_float(s[48 + 2 * i]), __uint_as_float(s[48 + 2 * i + 1]));
   }
-  return fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+  return fmax3(fmaxf(m0, m1), m2, m3);
 }
 
 __device__ __forceinline__ void rescale_accumulator(uint32_t tO, float alpha) {
@@ -360,17 +360,25 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
           rescale_accumulator(tO, alpha);
         }
       }
+      // p = 2^(s * scale - m_ref), two keys per FMA / add instruction; the row sum uses the unrounded values
       uint32_t pk[64];
-      float sum0 = 0.f, sum1 = 0.f;
+      {
+        const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
+        f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0 = ex2_approx(fmaf(__uint_as_float(s[2 * i]), scale, -m_ref));
-        const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), scale, -m_ref));
-        sum0 += p0;
-        sum1 += p1;
-        pk[i] = pack_p(p0, p1);
+        for (int i = 0; i < 64; ++i) {
+          const f32x2 x = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
+          float x0, x1;
+          unpack2(x, x0, x1);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          sum2[i & 1] = add2(sum2[i & 1], pack2(p0, p1));
+          pk[i] = pack_p(p0, p1);
+        }
+        float sa, sb, sc, sd;
+        unpack2(sum2[0], sa, sb);
+        unpack2(sum2[1], sc, sd);
+        l_run += (sa + sb) + (sc + sd);
       }
-      l_run += sum0 + sum1;
       tmem_st32_at<0>(tS, pk);
       tmem_st32_at<32>(tS + 32, pk);
       tmem_st_wait();
