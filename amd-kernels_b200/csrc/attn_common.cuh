@@ -66,6 +66,25 @@ struct LiteParams {
   float threshold;           // log2 units, negative
 };
 
+// MLA absorbed-decode launch (mla_decode.cu).
+struct MlaParams {
+  const void* q_lat;      // bf16 [B, q_len, H, 512]  ([B, H, 512] when q_len = 1)
+  const void* q_pe;       // bf16 [B, q_len, H, 64]
+  const void* kv;         // fp8 rows of 576 bytes: [B, seq, 576] or a pool [slots, 1, 576]
+  void* o_lat;            // bf16, like q_lat
+  const int* seq_lens;    // [B] cached tokens per request, or null (= seq)
+  const int* rows;        // [B] batch row of q / o for request b, or null (= b)
+  const int* kv_indices;  // flat per-token slots, or null (contiguous slab)
+  const int* kv_indptr;   // [B + 1] offsets into kv_indices
+  uint32_t* status;
+  float* part_o;          // [B * groups * parts][16 * pos_per_cta][512] un-normalised partial outputs
+  float* part_ml;         // [B * groups * parts][16 * pos_per_cta][2] reference maximum (log2 units), denominator
+  int batch, heads, q_len, seq;
+  int parts, groups, pos_per_cta;
+  int kv_format;          // 0: e4m3-fnuz (the reference's), 1: e4m3 (OCP, what the tensor core reads)
+  float scale, kv_scale;
+};
+
 // ---------------------------------------------------------------------------
 // bounded waits
 // ---------------------------------------------------------------------------

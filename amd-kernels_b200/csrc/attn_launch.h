@@ -12,6 +12,7 @@ namespace ma {
 
 struct AttnParams;
 struct LiteParams;
+struct MlaParams;
 
 // One CTA per 128-row query tile, fully serialised (cross-check kernel).
 cudaError_t launch_attn_simple(const AttnParams& p, cudaStream_t stream);
@@ -27,6 +28,9 @@ cudaError_t launch_merge_parts(const AttnParams& p, cudaStream_t stream);
 // (and zeroes the hand-out counter).
 cudaError_t launch_attn_lite(const LiteParams& p, int grid, cudaStream_t stream);
 cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stream);
+
+// MLA absorbed decode: one CTA per (request, group of draft positions, KV part), then the merge of the parts.
+cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream);
 
 // dst[i] = bf16(src[i]) with the given rounding mode (device pointers); exposes the
 // epilogue's rounding code for exhaustive bit-pattern tests.

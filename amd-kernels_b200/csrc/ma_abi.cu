@@ -122,6 +122,7 @@ const char* ma_error_string(int rc) {
     case MA_ERR_DEVICE: return "current CUDA device is not an sm_100 GPU";
     case MA_ERR_TOO_LARGE: return "problem exceeds the kernel's index range";
     case MA_ERR_LITE_ARGS: return "threshold must be negative, phase 0 or 1, at most 32766 key blocks of 64";
+    case MA_ERR_MLA_ARGS: return "parts must be in [1, MA_MLA_MAX_PARTS], kv_format 0 (e4m3-fnuz) or 1 (e4m3)";
     case MA_ERR_STATIC_SCRATCH:
       return "problem needs more scratch than the built-in static buffer holds (pass MA_FLAG_NO_TAIL or use "
              "ma_attention_forward with a workspace)";
@@ -334,6 +335,76 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
   }
   const int grid = p.num_tasks < sms ? p.num_tasks : sms;
   return cuda_rc(ma::launch_attn_lite(p, grid, stream));
+}
+
+// ---- MLA absorbed decode -------------------------------------------------------------------------------
+namespace {
+// Draft positions per CTA.  One: a window of q_len positions is q_len CTAs per (request, KV part) that read
+// the same KV rows, the later ones from L2 (the reference's q_len = 1 kernel does the same,
+// csrc/mla_decode_a16w8.hip "QLC=1").  The kernel template also takes two, but its softmax then keeps twice
+// the per-row state in registers and measured slower.
+int mla_pos_per_cta(int) { return 1; }
+int mla_groups(int q_len) { return (q_len + mla_pos_per_cta(q_len) - 1) / mla_pos_per_cta(q_len); }
+}  // namespace
+
+int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms) {
+  if (batch <= 0 || q_len < 1 || q_len > 8 || max_seq_len <= 0) return 1;
+  const int sms = resolve_sms(num_sms);
+  if (sms <= 0) return 1;
+  const int base = batch * mla_groups(q_len);             // CTAs before any split
+  const int tiles = (max_seq_len + 127) / 128;            // 128-token tiles of the longest request
+  int parts = sms / base;                                 // fill the GPU once ...
+  const int by_length = (tiles + 3) / 4;                  // ... with at least four tiles (512 tokens) per part
+  if (parts > by_length) parts = by_length;
+  if (parts > MA_MLA_MAX_PARTS) parts = MA_MLA_MAX_PARTS;
+  return parts < 1 ? 1 : parts;
+}
+
+size_t ma_mla_workspace_bytes(int batch, int q_len, int parts) {
+  if (batch <= 0 || q_len < 1 || q_len > 8 || parts < 1) return ma::kStatusBytes;
+  const size_t slots = static_cast<size_t>(batch) * mla_groups(q_len) * parts;
+  const size_t rows = 16u * mla_pos_per_cta(q_len);
+  return ma::kStatusBytes + slots * rows * (512 + 2) * sizeof(float);
+}
+
+int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
+                        const int* rows, const int* kv_indices, const int* kv_indptr, int batch, int heads, int q_len,
+                        int seq_len, int parts, float scale, float kv_scale, int kv_format, void* workspace,
+                        size_t workspace_bytes, void* stream_) {
+  if (batch <= 0 || heads < 1 || heads > 16) return MA_ERR_BATCH_HEADS;
+  if (q_len < 1 || q_len > 8) return MA_ERR_SEQ_Q;
+  const bool paged = kv_indices != nullptr;
+  if (paged ? (kv_indptr == nullptr || seq_lens == nullptr) : seq_len <= 0) return MA_ERR_SEQ_KV;
+  if (parts < 1 || parts > MA_MLA_MAX_PARTS || (kv_format != 0 && kv_format != 1)) return MA_ERR_MLA_ARGS;
+  if (q_lat == nullptr || q_pe == nullptr || kv == nullptr || o_lat == nullptr) return MA_ERR_NULL_POINTER;
+  const uintptr_t bits = reinterpret_cast<uintptr_t>(q_lat) | reinterpret_cast<uintptr_t>(q_pe) |
+                         reinterpret_cast<uintptr_t>(kv) | reinterpret_cast<uintptr_t>(o_lat);
+  if (bits & 15u) return MA_ERR_ALIGNMENT;
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) ||
+      workspace_bytes < ma_mla_workspace_bytes(batch, q_len, parts))
+    return MA_ERR_WORKSPACE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int dev = 0, major = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (major != 10) return MA_ERR_DEVICE;
+
+  ma::MlaParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q_lat = q_lat, p.q_pe = q_pe, p.kv = kv, p.o_lat = o_lat;
+  p.seq_lens = seq_lens, p.rows = rows, p.kv_indices = kv_indices, p.kv_indptr = kv_indptr;
+  p.batch = batch, p.heads = heads, p.q_len = q_len, p.seq = seq_len;
+  p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len), p.groups = mla_groups(q_len);
+  p.kv_format = kv_format, p.scale = scale, p.kv_scale = kv_scale;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  p.status = reinterpret_cast<uint32_t*>(ws);
+  const size_t slots = static_cast<size_t>(batch) * p.groups * parts, r = 16u * p.pos_per_cta;
+  p.part_ml = reinterpret_cast<float*>(ws + ma::kStatusBytes);
+  p.part_o = p.part_ml + slots * r * 2;
+  e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+  return cuda_rc(ma::launch_mla_decode(p, stream));
 }
 
 int ma_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, void* stream) {

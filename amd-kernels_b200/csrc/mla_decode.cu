@@ -1,0 +1,668 @@
+// MLA absorbed-decode attention, bf16 queries against an fp8 KV cache ("A16W8"), for sm_100a.
+//
+// What it computes is the reference's mla_decode_a16w8 / _multiq operators (csrc/mla_decode_a16w8.hip:186,
+// csrc/mla_decode_a16w8_multiq.hip:722; semantics stated in moonmath_attention/mla.py:41-186 and
+// tests/test_mla_decode.py:52-68): per request b and draft position t, softmax over the first
+// len_b - q_len + t + 1 cached tokens of (q_lat . kv[:512] + q_pe . kv[512:576]) * scale, times kv[:512],
+// with kv stored as fp8 rows of 576 bytes at one per-tensor scale, contiguous or paged one token per slot.
+//
+// How: the KV bytes go to the tensor core as they are.  The reference unpacks fp8 to bf16 on the way into
+// LDS; here a tile of 128 tokens x 576 bytes is the A operand of fp8 MMAs (kind::f8f6f4) twice:
+//   S^T[128 tokens x N]   = KV[128 x 576] (K-major)  x  Q^T[576 x N]
+//   O^T[4 x 128 dims x N] = KV^T (same bytes, MN-major, 128 latent bytes of a row per M tile)  x  P^T[128 tokens x N]
+// The 16-bit operands become sums of two e4m3 terms, stacked along N (N = 2 x rows): a query row scaled by a
+// power of two splits exactly into q1 + q2 (8 significant bits = 4 + 4); a probability splits the same
+// way (the reference rounds it to bf16, also 8 bits).  The terms' partial sums sit in separate accumulator
+// columns and are added by the thread that reads them.  With tokens on the lanes of tensor memory, a thread
+// owns one token (softmax) or one output dimension (rescale, epilogue).
+//
+// e4m3-fnuz (the reference's format) differs from the e4m3 the tensor core reads by a factor of two in
+// every finite value, folded into the scales, and in two codes: 0x7F / 0xFF are +-240 there and NaN here,
+// so the loader rewrites them to 0x7E / 0xFE (+-224: the one approximation of this kernel, on saturated
+// cache entries only); 0x80 (NaN there) reads as zero.  e4m3 caches (kv_format 1) are read unchanged.
+//
+// One CTA per (request, group of draft positions, KV part); parts are merged by mla_merge_kernel.
+//   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12  copy    warps 13-16  check
+// All waits are bounded mbarrier waits.
+#include <cuda_fp8.h>
+
+#include "attn_common.cuh"
+#include "attn_launch.h"
+
+namespace ma {
+namespace {
+
+using namespace sm100;
+
+constexpr int kLat = 512, kRowBytes = 576;
+constexpr int kTok = 128;                        // tokens per tile
+constexpr int kChunks = 5;                       // 128-byte column chunks of a row: 4 latent + rope (64 bytes used)
+constexpr int kChunkBytes = kTok * 128;          // 16 KiB
+constexpr int kTileBytesMla = kChunks * kChunkBytes;
+constexpr int kStagesMla = 2;
+constexpr int kHeadsMax = 16;
+constexpr int kSoftmaxThreads = 128, kCopyThreads = 256, kCheckThreads = 128;
+constexpr int kThreadsMla = kSoftmaxThreads + 32 + kCopyThreads + kCheckThreads;  // 544
+constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
+
+template <int kPos>
+struct Cfg {
+  static constexpr int kRows = kHeadsMax * kPos;  // query rows per CTA
+  static constexpr int kN = 2 * kRows;            // two e4m3 terms per row
+  static constexpr uint32_t kTmemCols = kPos == 1 ? 256 : 512;  // S x 2 + O^T x 4 = 6 * kN = 192 / 384
+  static constexpr uint32_t kOffKV = 0;
+  static constexpr uint32_t kOffQT = kStagesMla * kTileBytesMla;       // [5 chunks][kN rows][128 B]
+  static constexpr uint32_t kOffPT = kOffQT + kChunks * kN * 128;      // [2][kN rows][128 B]
+  static constexpr uint32_t kOffRowScale = kOffPT + 2 * kN * 128;      // float [kRows]: score = (S1 + S2) * this
+  static constexpr uint32_t kOffMx = kOffRowScale + kRows * 4;         // float [2][4 warps][kRows]
+  static constexpr uint32_t kOffL = kOffMx + 2 * 4 * kRows * 4;        // float [4 warps][kRows]: denominators (epilogue)
+  static constexpr uint32_t kOffFlags = kOffL + 4 * kRows * 4;         // int [2][4 warps]
+  static constexpr uint32_t kOffBars = kOffFlags + 2 * 4 * 4;
+};
+enum MlaBar : uint32_t {
+  kMTileFull = 0,   // [2] check warps -> MMA (128 arrivals)
+  kMTileEmpty = 2,  // [2] MMA -> loaders
+  kMSFull = 4,      // [2] MMA -> softmax
+  kMPFull = 6,      // [2] softmax -> MMA (128 arrivals)
+  kMPvDone = 8,     // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
+  kMMx = 10,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
+  kMFlag = 12,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
+  kMEpi = 14,       //     softmax warps among themselves: denominators written (4 arrivals)
+  kMTileRaw = 15,   // [2] copy warps -> check warps: the tile's copies have landed (128 arrivals)
+  kMNumBars = 17
+};
+
+#ifdef MA_TRACE
+// Development-only timestamp trace (built into a separate library, never into the product build).
+__device__ unsigned long long g_trace_mla[8192];
+#define MLA_TRACE_AT(slot, cond)                                                      \
+  do {                                                                                \
+    if ((cond) && blockIdx.x == 0 && (slot) < 8192) g_trace_mla[(slot)] = clock64(); \
+  } while (0)
+#else
+#define MLA_TRACE_AT(slot, cond) \
+  do {                           \
+  } while (0)
+#endif
+
+#define MA_WAIT(bar, parity, site) \
+  if (!mbar_wait((bar), (parity), (site), ctx)) return
+#define MA_WAIT_WARP(bar, parity, site) \
+  if (!mbar_wait_warp((bar), (parity), (site), ctx)) return
+#define MA_WAIT_SLEEP(ns, bar, parity, site) \
+  if (!mbar_wait<ns>((bar), (parity), (site), ctx)) return
+
+__device__ __forceinline__ void umma_ss_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Two floats -> two e4m3 bytes (round to nearest, saturating), low byte = first argument; and back.
+__device__ __forceinline__ uint32_t to_e4m3x2(float lo, float hi) {
+  return __nv_cvt_float2_to_fp8x2(make_float2(lo, hi), __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ float2 from_e4m3x2(uint32_t v) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(v), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
+// Byte offset of (row, byte column) inside a [rows][128 B] block with the 128-byte swizzle.
+__device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t col) {
+  return row * 128u + ((((col >> 4) ^ (row & 7u)) << 4) | (col & 15u));
+}
+
+struct Work {
+  int b, brow, group, part;
+  int q_len, heads;
+  int pos0, npos;       // draft positions of this CTA
+  int len;              // cached tokens of the request
+  int tile0, tiles;     // tiles [tile0, tile0 + tiles) of 128 tokens
+  int end_max;          // tokens the last position of the group may see
+};
+
+__device__ __forceinline__ Work decode_work(const MlaParams& p, int kpos) {
+  Work w;
+  const int cta = blockIdx.x;
+  w.part = cta % p.parts;
+  const int bg = cta / p.parts;
+  w.group = bg % p.groups;
+  w.b = bg / p.groups;
+  w.brow = p.rows != nullptr ? p.rows[w.b] : w.b;
+  w.q_len = p.q_len;
+  w.heads = p.heads;
+  w.pos0 = w.group * kpos;
+  w.npos = min(kpos, p.q_len - w.pos0);
+  w.len = p.seq_lens != nullptr ? p.seq_lens[w.b] : p.seq;
+  w.end_max = w.len - p.q_len + w.pos0 + w.npos;  // last position of the group, inclusive limit + 1
+  const int total = w.end_max > 0 ? (w.end_max + kTok - 1) / kTok : 0;
+  const int per = (total + p.parts - 1) / p.parts;
+  w.tile0 = min(w.part * per, total);
+  w.tiles = min(per, total - w.tile0);
+  return w;
+}
+
+// ---------------------------------------------------------------------------
+// loaders.  Eight "copy" warps stream a tile of 128 token rows into the swizzled chunks with 16-byte
+// asynchronous copies (no registers in between) and hand completion to an mbarrier, so they never wait for
+// data and the next tile's copies start the moment its stage is free.  Four "check" warps take the landed
+// tile, rewrite the byte codes that need it (e4m3-fnuz only), make the tile visible to the tensor core and
+// pass it on.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The mbarrier receives one arrival once every copy this thread has issued so far has landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int kPos>
+__device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uint32_t base, int lt, const WaitCtx& ctx) {
+  using C = Cfg<kPos>;
+  const uint32_t bars = base + C::kOffBars;
+  const uint8_t* kv = static_cast<const uint8_t*>(p.kv);
+  const int idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
+  constexpr int kPerThread = kTok * (kRowBytes / 16) / kCopyThreads;  // 18 copies per tile
+  for (int j = 0; j < w.tiles; ++j) {
+    if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + (j & 1)), ((j >> 1) - 1) & 1, 0x50);
+    MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
+    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const int tok0 = (w.tile0 + j) * kTok;
+#pragma unroll
+    for (int i = 0; i < kPerThread; ++i) {
+      const int id = i * kCopyThreads + lt;
+      const int tok = id / 36, q = id % 36;
+      const int tok_abs = tok0 + tok;
+      const bool live = tok_abs < w.end_max;  // rows past the end are zero-filled (source size 0)
+      const size_t slot = !live ? 0
+                          : p.kv_indices != nullptr ? static_cast<size_t>(p.kv_indices[idx0 + tok_abs])
+                                                    : static_cast<size_t>(w.b) * p.seq + tok_abs;
+      const uint32_t col = static_cast<uint32_t>(q) * 16u;
+      cp_async16(tile + (col >> 7) * kChunkBytes + swz128(tok, col & 127u), kv + slot * kRowBytes + col, live ? 16u : 0u);
+    }
+    cp_async_arrive(bars + 8 * (kMTileRaw + (j & 1)));
+    MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
+  }
+}
+
+template <int kPos>
+__device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, uint32_t base, uint8_t* smem, int lt,
+                                           const WaitCtx& ctx) {
+  using C = Cfg<kPos>;
+  const uint32_t bars = base + C::kOffBars;
+  const bool fnuz = p.kv_format == 0;
+  constexpr int kPerThread = kTileBytesMla / 16 / kCheckThreads;  // 40 x 16 bytes per tile (the rope chunk's unused half included)
+  for (int j = 0; j < w.tiles; ++j) {
+    MA_WAIT_SLEEP(32, bars + 8 * (kMTileRaw + (j & 1)), (j >> 1) & 1, 0x58);
+    MLA_TRACE_AT(4000 + j * 4 + 2, lt == 0 && j < 60);
+    if (fnuz) {
+      // 0x7F / 0xFF (+-240 in e4m3-fnuz) are NaN to the tensor core: one code down (+-224).  First pass: is any
+      // such byte among this thread's share?  (Hardly ever.)  Only then a second pass rewrites.
+      uint4* tile = reinterpret_cast<uint4*>(smem + C::kOffKV + (j & 1) * kTileBytesMla);
+      uint32_t any = 0;
+#pragma unroll 8
+      for (int i = 0; i < kPerThread; ++i) {
+        const uint4 v = tile[i * kCheckThreads + lt];
+        any |= ((v.x & 0x7F7F7F7Fu) + 0x01010101u) | ((v.y & 0x7F7F7F7Fu) + 0x01010101u) |
+               ((v.z & 0x7F7F7F7Fu) + 0x01010101u) | ((v.w & 0x7F7F7F7Fu) + 0x01010101u);
+      }
+      if (any & 0x80808080u) {
+        for (int i = 0; i < kPerThread; ++i) {
+          uint4 v = tile[i * kCheckThreads + lt];
+          uint32_t* x = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) x[k] -= (((x[k] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u) >> 7;
+          tile[i * kCheckThreads + lt] = v;
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    mbar_arrive(bars + 8 * (kMTileFull + (j & 1)));
+    MLA_TRACE_AT(4000 + j * 4 + 3, lt == 0 && j < 60);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// MMA issuer (one thread)
+// ---------------------------------------------------------------------------
+template <int kPos>
+__device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
+  using C = Cfg<kPos>;
+  constexpr uint32_t kFmtE4M3 = 0;
+  constexpr uint32_t idesc_qk = umma_idesc(kFmtE4M3, kFmtE4M3, 0, 0, kTok, C::kN);
+  constexpr uint32_t idesc_pv = umma_idesc(kFmtE4M3, kFmtE4M3, 1, 0, kTok, C::kN);
+  const uint32_t bars = base + C::kOffBars;
+  const uint32_t qt_lo = desc_lo_kmajor(base + C::kOffQT);
+  const int n = w.tiles;
+  auto issue_qk = [&](int j) {
+    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const uint32_t a_lo = desc_lo_kmajor(tile);
+    const uint32_t d = tmem + (j & 1) * C::kN;
+#pragma unroll
+    for (int c = 0; c < kChunks; ++c) {
+#pragma unroll
+      for (int ks = 0; ks < (c < 4 ? 4 : 2); ++ks) {
+        umma_ss_f8(d, make_desc(a_lo + ((c * kChunkBytes + ks * 32) >> 4)),
+                   make_desc(qt_lo + ((c * C::kN * 128 + ks * 32) >> 4)), idesc_qk, (c | ks) != 0 ? 1u : 0u);
+      }
+    }
+    umma_commit(bars + 8 * (kMSFull + (j & 1)));
+  };
+  auto issue_pv = [&](int j) {
+    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const uint32_t pt_lo = desc_lo_kmajor(base + C::kOffPT + (j & 1) * C::kN * 128);
+#pragma unroll
+    for (int mt = 0; mt < 4; ++mt) {
+      // A = 128 latent bytes of every token row (M), 32 token rows per step (K): MN-major, one swizzle atom wide
+      const uint32_t a_lo = desc_lo_mnmajor<kTok>(tile + mt * kChunkBytes);
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        umma_ss_f8(tmem + (2 + mt) * C::kN, make_desc(a_lo + ((ks * 32 * 128) >> 4)), make_desc(pt_lo + ((ks * 32) >> 4)),
+                   idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+      }
+    }
+    umma_commit(bars + 8 * (kMTileEmpty + (j & 1)));
+    umma_commit(bars + 8 * (kMPvDone + (j & 1)));
+  };
+  // Whatever is ready is issued: Q K^T of tile i needs the tile and the S buffer (read out by the softmax of
+  // tile i - 2, known from its P arrival, i.e. once P V (i - 2) has been issued); P V of tile j needs P(j).
+  int qk_i = 0, pv_i = 0;
+  uint32_t idle = 0;
+  uint64_t t0 = 0;
+  while (pv_i < n) {
+    bool progressed = false;
+    if (qk_i < n && qk_i - pv_i < 2 && mbar_test_wait(bars + 8 * (kMTileFull + (qk_i & 1)), (qk_i >> 1) & 1)) {
+      tc_fence_after_sync();
+      MLA_TRACE_AT(2000 + qk_i * 8 + 1, qk_i < 60);
+      issue_qk(qk_i);
+      MLA_TRACE_AT(2000 + qk_i * 8 + 2, qk_i < 60);
+      ++qk_i;
+      progressed = true;
+    }
+    if (pv_i < qk_i && mbar_test_wait(bars + 8 * (kMPFull + (pv_i & 1)), (pv_i >> 1) & 1)) {
+      tc_fence_after_sync();
+      MLA_TRACE_AT(2000 + pv_i * 8 + 3, pv_i < 60);
+      issue_pv(pv_i);
+      MLA_TRACE_AT(2000 + pv_i * 8 + 4, pv_i < 60);
+      ++pv_i;
+      progressed = true;
+    }
+    if (progressed) {
+      idle = 0;
+      t0 = 0;
+    } else if ((++idle & 0x3FFu) == 0u) {  // bounded like every other wait
+      if (*ctx.abort) return;
+      if (ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
+        *ctx.abort = 1;
+        return;
+      }
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
+        record_error(ctx.status, kErrWaitTimeout, 0x60, (static_cast<uint32_t>(qk_i) << 16) | static_cast<uint32_t>(pv_i));
+        *ctx.abort = 1;
+        return;
+      }
+    }
+  }
+}
+
+// Orders floats as signed integers (for redux.sync.max).
+__device__ __forceinline__ int float_key(float f) {
+  const int i = __float_as_int(f);
+  return i ^ ((i >> 31) & 0x7FFFFFFF);
+}
+__device__ __forceinline__ float key_float(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7FFFFFFF)); }
+
+template <int kCols>
+__device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&d)[kCols]) {
+  if constexpr (kCols == 32) {
+    tmem_ld32_sync(taddr, d);
+  } else {
+    tmem_ld64_sync(taddr, d);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// softmax warps: thread = token of the tile (S^T lanes) and = output dimension (O^T lanes)
+//
+// The reference maximum of a row moves lazily (by more than tau above it, and on the first tile), so that
+// p <= 2^tau = 256 fits e4m3.  A tile normally needs no maximum at all: every thread checks its own scores
+// against reference + tau, the four warps exchange one flag, and only a raised flag sends the CTA through
+// the exact row maxima (redux + a second exchange) and the rescale of O^T.  All of this is uniform over the
+// CTA: every thread holds the same reference maxima.  The softmax denominator is summed per thread (one
+// token each) over all tiles and reduced across the threads once, in the epilogue.
+// ---------------------------------------------------------------------------
+template <int kPos>
+__device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, uint8_t* smem, uint32_t base,
+                                             uint32_t tmem, int tl, const WaitCtx& ctx) {
+  using C = Cfg<kPos>;
+  constexpr int R = C::kRows, N = C::kN;
+  const uint32_t bars = base + C::kOffBars;
+  const uint32_t lane_sel = static_cast<uint32_t>(tl & ~31) << 16;
+  const int warp = tl >> 5, lane = tl & 31;
+  const float* row_scale = reinterpret_cast<const float*>(smem + C::kOffRowScale);
+  float* mx = reinterpret_cast<float*>(smem + C::kOffMx);          // [2][4][R] row maxima of a tile, per warp
+  volatile int* flags = reinterpret_cast<volatile int*>(smem + C::kOffFlags);  // [2][4] "a score is above reference + tau"
+  float* l_part = reinterpret_cast<float*>(smem + C::kOffL);       // [4][R] per-warp denominators (epilogue)
+  const int n = w.tiles;
+  float m_ref[R], l_sum[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) m_ref[r] = 0.f, l_sum[r] = 0.f;
+  uint32_t slow = 0;  // exact-maximum rounds so far (phase of their barrier)
+
+  for (int j = 0; j < n; ++j) {
+    const int buf = j & 1, par = (j >> 1) & 1;
+    const bool tr = tl == 0 && j < 60;
+    MLA_TRACE_AT(j * 8 + 0, tr);
+    MA_WAIT_WARP(bars + 8 * (kMSFull + buf), par, 0x70);
+    MLA_TRACE_AT(j * 8 + 1, tr);
+    tc_fence_after_sync();
+    uint32_t d[N];
+    tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
+    const int tok_abs = (w.tile0 + j) * kTok + tl;
+    float s[R];
+    float over = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      // position (r / 16) of the group sees tokens [0, len - q_len + pos + 1)
+      const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
+      const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * row_scale[r];
+      s[r] = tok_abs < limit ? v : -INFINITY;
+      over = fmaxf(over, s[r] - m_ref[r]);
+    }
+    const bool warp_over = __any_sync(0xffffffffu, over > kTauMla) || j == 0;
+    if (lane == 0) {
+      flags[buf * 4 + warp] = warp_over ? 1 : 0;
+      mbar_arrive(bars + 8 * (kMFlag + buf));
+    }
+    MLA_TRACE_AT(j * 8 + 2, tr);
+    MA_WAIT_WARP(bars + 8 * (kMFlag + buf), par, 0x71);
+    MLA_TRACE_AT(j * 8 + 3, tr);
+    if ((flags[buf * 4 + 0] | flags[buf * 4 + 1] | flags[buf * 4 + 2] | flags[buf * 4 + 3]) != 0) {
+      // exact row maxima of the tile: redux within the warp, shared memory across the four warps
+      const int sb = slow & 1;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int k = __reduce_max_sync(0xffffffffu, float_key(s[r]));
+        if (lane == (r & 31)) mx[(sb * 4 + warp) * R + r] = key_float(k);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kMMx + sb));
+      MA_WAIT_WARP(bars + 8 * (kMMx + sb), (slow >> 1) & 1, 0x75);
+      ++slow;
+      float alpha[R];
+      bool moved = false;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const float* m4 = mx + sb * 4 * R + r;
+        const float m_tile = fmaxf(fmaxf(m4[0], m4[R]), fmaxf(m4[2 * R], m4[3 * R]));
+        float m_new = m_ref[r];
+        if (j == 0) {
+          m_new = (m_tile == -INFINITY) ? 0.f : m_tile;
+        } else if (m_tile - m_ref[r] > kTauMla) {
+          m_new = m_tile;
+        }
+        alpha[r] = ex2_approx(m_ref[r] - m_new);
+        moved = moved || (m_new != m_ref[r]);
+        m_ref[r] = m_new;
+        l_sum[r] *= alpha[r];
+      }
+      if (j > 0 && moved) {
+        MA_WAIT_WARP(bars + 8 * (kMPvDone + ((j - 1) & 1)), ((j - 1) >> 1) & 1, 0x72);
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int mt = 0; mt < 4; ++mt) {
+          uint32_t o[N];
+          tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
+#pragma unroll
+          for (int c = 0; c < N; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c % R]);
+          if constexpr (N == 32) {
+            tmem_st32(tmem + (2 + mt) * N + lane_sel, o);
+          } else {
+            tmem_st32_at<0>(tmem + (2 + mt) * N + lane_sel, o);
+            tmem_st32_at<32>(tmem + (2 + mt) * N + lane_sel + 32, o);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+      }
+    }
+    // probabilities as two e4m3 terms each; rows are converted in pairs
+    uint32_t t1[R / 2], t2[R / 2];
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      const float p0 = ex2_approx(s[r] - m_ref[r]), p1 = ex2_approx(s[r + 1] - m_ref[r + 1]);
+      l_sum[r] += p0;
+      l_sum[r + 1] += p1;
+      t1[r / 2] = to_e4m3x2(p0, p1);
+      const float2 back = from_e4m3x2(t1[r / 2]);
+      t2[r / 2] = to_e4m3x2(p0 - back.x, p1 - back.y);
+    }
+    MLA_TRACE_AT(j * 8 + 4, tr);
+    if (j >= 2) MA_WAIT_WARP(bars + 8 * (kMPvDone + buf), ((j - 2) >> 1) & 1, 0x73);
+    MLA_TRACE_AT(j * 8 + 5, tr);
+    uint8_t* pt = smem + C::kOffPT + buf * N * 128;
+#pragma unroll
+    for (int r = 0; r < R; r += 2) {
+      pt[swz128(r, tl)] = static_cast<uint8_t>(t1[r / 2] & 0xFF);
+      pt[swz128(r + 1, tl)] = static_cast<uint8_t>(t1[r / 2] >> 8);
+      pt[swz128(R + r, tl)] = static_cast<uint8_t>(t2[r / 2] & 0xFF);
+      pt[swz128(R + r + 1, tl)] = static_cast<uint8_t>(t2[r / 2] >> 8);
+    }
+    fence_proxy_async_smem();
+    tc_fence_before_sync();
+    mbar_arrive(bars + 8 * (kMPFull + buf));
+    MLA_TRACE_AT(j * 8 + 6, tr);
+  }
+
+  // epilogue: un-normalised fp32 partial outputs, reference maximum and denominator of every row
+  const size_t slot = blockIdx.x;
+  float* part_o = p.part_o + slot * (static_cast<size_t>(R) * kLat);
+  float2* part_ml = reinterpret_cast<float2*>(p.part_ml) + slot * R;
+  if (n == 0) {
+    if (tl < R) part_ml[tl] = make_float2(-INFINITY, 0.f);
+    return;
+  }
+  // denominators: sum over the 128 tokens-of-a-tile threads
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float v = l_sum[r];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if (lane == (r & 31)) l_part[warp * R + r] = v;
+  }
+  MA_WAIT_WARP(bars + 8 * (kMPvDone + ((n - 1) & 1)), ((n - 1) >> 1) & 1, 0x74);
+  tc_fence_after_sync();
+#pragma unroll 1
+  for (int mt = 0; mt < 4; ++mt) {
+    uint32_t o[N];
+    tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
+  }
+  // the four warps' denominators meet through shared memory; the flag barrier of the unused parity orders them
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bars + 8 * kMEpi);
+  MA_WAIT_WARP(bars + 8 * kMEpi, 0, 0x76);
+  if (tl < R) {
+    const float l = (l_part[tl] + l_part[R + tl]) + (l_part[2 * R + tl] + l_part[3 * R + tl]);
+    float m = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (r == tl) m = m_ref[r];
+    part_ml[tl] = make_float2(m, l);
+  }
+}
+
+template <int kPos>
+__global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
+  using C = Cfg<kPos>;
+  constexpr int R = C::kRows, N = C::kN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t base = smem_u32(smem);
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const WaitCtx ctx{p.status, abort_flag};
+  const Work w = decode_work(p, kPos);
+
+  if (tid == 0) {
+    const uint32_t bars = base + C::kOffBars;
+    for (uint32_t i = 0; i < kMNumBars; ++i) {
+      uint32_t count = 1;
+      if (i >= kMTileFull && i < kMTileFull + 2) count = kCheckThreads;
+      if (i >= kMTileRaw && i < kMTileRaw + 2) count = kCopyThreads;
+      if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
+      if (i >= kMMx && i <= kMEpi) count = 4;
+      mbar_init(bars + 8 * i, count);
+    }
+    abort_flag_s = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+
+  // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a row
+  // is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
+  // q * f = q1 + q2 exact for every element within 2^-7 of the largest (8 significant bits = 4 + 4).
+  {
+    const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
+    const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
+    float* row_scale = reinterpret_cast<float*>(smem + C::kOffRowScale);
+    uint8_t* qt = smem + C::kOffQT;
+    const float fmt = p.kv_format == 0 ? 2.f : 1.f;  // e4m3-fnuz bytes read as e4m3 are twice their value
+    for (int r = warp; r < R; r += kThreadsMla / 32) {
+      const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
+      const bool live = h < w.heads && pos < w.q_len;
+      const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
+      float v[18];  // 576 / 32
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 18; ++i) {
+        const int x = i * 32 + lane;
+        v[i] = !live ? 0.f : (x < kLat ? __bfloat162float(q_lat[qrow * kLat + x]) : __bfloat162float(q_pe[qrow * 64 + (x - kLat)]));
+        amax = fmaxf(amax, fabsf(v[i]));
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      // f = 2^(7 - exponent(amax)); NaN / inf / zero rows keep f = 1
+      float f = 1.f;
+      if (amax > 0.f && amax < INFINITY) {
+        const int e = static_cast<int>((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+        f = __uint_as_float(static_cast<uint32_t>(127 + 7 - e) << 23);
+      }
+      if (lane == 0) row_scale[r] = p.scale * 1.4426950408889634f * p.kv_scale / (fmt * f);
+#pragma unroll
+      for (int i = 0; i < 18; i += 2) {
+        const float a = v[i] * f, b = v[i + 1] * f;
+        const uint32_t t1 = to_e4m3x2(a, b);
+        const float2 back = from_e4m3x2(t1);
+        const uint32_t t2 = to_e4m3x2(a - back.x, b - back.y);
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t x = (i + k) * 32 + lane;
+          const uint32_t chunk = x >> 7, col = x & 127u;
+          qt[chunk * (N * 128) + swz128(r, col)] = static_cast<uint8_t>((t1 >> (8 * k)) & 0xFF);
+          qt[chunk * (N * 128) + swz128(R + r, col)] = static_cast<uint8_t>((t2 >> (8 * k)) & 0xFF);
+        }
+      }
+    }
+  }
+  fence_proxy_async_smem();
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp < 4) {
+    role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
+  } else if (warp == 4) {
+    if (lane == 0) role_mma<kPos>(w, base, tmem, ctx);
+  } else if (warp < 5 + kCopyThreads / 32) {
+    role_copy<kPos>(p, w, base, tid - (kSoftmaxThreads + 32), ctx);
+  } else {
+    role_check<kPos>(p, w, base, smem, tid - (kSoftmaxThreads + 32 + kCopyThreads), ctx);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem, C::kTmemCols);
+}
+
+// ---------------------------------------------------------------------------
+// merge of the KV parts: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, scaled back, rounded to bf16
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int kpos) {
+  const int R = kHeadsMax * kpos;
+  const int row = blockIdx.x;  // (b, pos, h)
+  const int h = row % p.heads, pos = (row / p.heads) % p.q_len, b = row / (p.heads * p.q_len);
+  const int brow = p.rows != nullptr ? p.rows[b] : b;
+  const int group = pos / kpos, r = (pos % kpos) * kHeadsMax + h;
+  const size_t slot0 = (static_cast<size_t>(b) * p.groups + group) * p.parts;
+  const float2* ml = reinterpret_cast<const float2*>(p.part_ml);
+  float m_all = -INFINITY;
+  for (int q = 0; q < p.parts; ++q) {
+    const float2 v = ml[(slot0 + q) * R + r];
+    if (v.y > 0.f || v.y != v.y) m_all = fmaxf(m_all, v.x);
+  }
+  float acc[4] = {0.f, 0.f, 0.f, 0.f}, l_all = 0.f;
+  for (int q = 0; q < p.parts; ++q) {
+    const float2 v = ml[(slot0 + q) * R + r];
+    if (!(v.y > 0.f || v.y != v.y)) continue;  // a part without tokens
+    const float wgt = ex2_approx(v.x - m_all);
+    l_all += wgt * v.y;
+    const float* o = p.part_o + ((slot0 + q) * R + r) * kLat;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] += wgt * o[k * 128 + threadIdx.x];
+  }
+  const float fmt = p.kv_format == 0 ? 2.f : 1.f;
+  const float inv = l_all > 0.f || l_all != l_all ? p.kv_scale / (fmt * l_all) : 0.f;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat) + ((static_cast<size_t>(brow) * p.q_len + pos) * p.heads + h) * kLat;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) out[k * 128 + threadIdx.x] = __float2bfloat16_rn(acc[k] * inv);
+}
+
+template <int kPos>
+cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
+  using C = Cfg<kPos>;
+  constexpr size_t smem_bytes = C::kOffBars + kMNumBars * 8 + 1024;
+  static_assert(smem_bytes <= 232448, "shared memory budget of one CTA on sm_100");
+  cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel<kPos>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem_bytes));
+  if (e != cudaSuccess) return e;
+  mla_decode_kernel<kPos><<<p.batch * p.groups * p.parts, kThreadsMla, smem_bytes, stream>>>(p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  mla_merge_kernel<<<p.batch * p.q_len * p.heads, 128, 0, stream>>>(p, kPos);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+#ifdef MA_TRACE
+extern "C" int ma_trace_read_mla(unsigned long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_mla, sizeof(unsigned long long) * n));
+}
+#endif
+
+cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
+  if (p.pos_per_cta != 1) return cudaErrorInvalidValue;  // only the one-position instance is built
+  return launch_one<1>(p, stream);
+}
+
+}  // namespace ma

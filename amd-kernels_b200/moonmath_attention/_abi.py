@@ -42,6 +42,9 @@ EXPORTS = (
     "ma_lite_workspace_bytes",
     "ma_lite_tile",
     "ma_attention_forward_lite",
+    "ma_mla_plan_parts",
+    "ma_mla_workspace_bytes",
+    "ma_mla_decode_a16w8",
 )
 
 
@@ -81,6 +84,14 @@ def _load() -> ctypes.CDLL:
     lib.ma_attention_forward_lite.restype = c_int
     lib.ma_attention_forward_lite.argtypes = (
         [c_void_p] * 4 + [c_int] * 7 + [c_void_p] * 3 + [ctypes.c_float, c_int, c_void_p, c_size_t, c_int, c_void_p]
+    )
+    lib.ma_mla_plan_parts.restype = c_int
+    lib.ma_mla_plan_parts.argtypes = [c_int] * 4
+    lib.ma_mla_workspace_bytes.restype = c_size_t
+    lib.ma_mla_workspace_bytes.argtypes = [c_int] * 3
+    lib.ma_mla_decode_a16w8.restype = c_int
+    lib.ma_mla_decode_a16w8.argtypes = (
+        [c_void_p] * 8 + [c_int] * 5 + [ctypes.c_float, ctypes.c_float, c_int, c_void_p, c_size_t, c_void_p]
     )
     if lib.ma_abi_version() != ABI_VERSION:
         raise ImportError(

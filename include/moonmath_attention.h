@@ -75,6 +75,7 @@ extern "C" {
 #define MA_ERR_TOO_LARGE 15      /* a dimension exceeds what the kernel indexes */
 #define MA_ERR_STATIC_SCRATCH 16 /* ma_attention_forward_static: the plan needs more than MA_STATIC_SCRATCH_BYTES */
 #define MA_ERR_LITE_ARGS 17      /* threshold >= 0, phase not 0 / 1, or more than 32766 key blocks of 64 */
+#define MA_ERR_MLA_ARGS 18       /* ma_mla_decode_a16w8: parts or kv_format out of range */
 #define MA_ERR_CUDA_BASE 1000    /* 1000 + cudaError_t of a failed runtime call or launch */
 
 /* Value of MA_ABI_VERSION the library was built with. */
@@ -183,6 +184,32 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
                               int seq_len_kv, int head_dim, int layout, int round_mode, const void* read_list,
                               void* write_list, const void* must_do_list, float threshold, int phase, void* workspace,
                               size_t workspace_bytes, int flags, void* stream);
+
+/*
+ * MLA absorbed-decode attention, bf16 queries against an fp8 KV cache.  One entry point for what the
+ * reference exports as launch_mla_decode_a16w8, launch_mla_decode_a16w8_paged_dev
+ * (csrc/mla_decode_a16w8.hip:784-876, bound from csrc/mla_decode_a16w8_api.cpp:76-150) and the multi-query
+ * pair (csrc/mla_decode_a16w8_multiq.hip:946-1001).
+ *   q_lat [batch][q_len][heads][512], q_pe [batch][q_len][heads][64], o_lat like q_lat: bf16, q_len 1..8,
+ *   heads 1..16.  Draft position t of request b attends the first len_b - q_len + t + 1 cached tokens.
+ *   kv: fp8 rows of 576 bytes ([0,512) latent, [512,576) rope), one per-tensor kv_scale.
+ *     contiguous: kv_indices = kv_indptr = null, kv is [batch][seq_len][576], len_b = seq_lens ? seq_lens[b] : seq_len;
+ *     paged:      kv is a pool [slots][576]; token i of request b lives in slot kv_indices[kv_indptr[b] + i];
+ *                 seq_lens is required.  All index arrays are int32 device memory, read by the kernel only
+ *                 (no host read, fixed grid: the call can be captured in a CUDA graph with `parts` fixed).
+ *   rows: optional int32[batch], batch row of q_lat / o_lat that request b uses (null: b).
+ *   kv_format: 0 = e4m3-fnuz, the reference's cache format; 1 = e4m3 (OCP).  The tensor core reads e4m3: fnuz
+ *     bytes are reinterpreted (every finite value is exactly half), except 0x7F / 0xFF (+-240) which are
+ *     rewritten to +-224, and 0x80 (NaN) which reads as zero.
+ *   parts: KV split per request, 1..MA_MLA_MAX_PARTS (ma_mla_plan_parts); workspace: ma_mla_workspace_bytes.
+ */
+#define MA_MLA_MAX_PARTS 64
+int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
+size_t ma_mla_workspace_bytes(int batch, int q_len, int parts);
+int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
+                        const int* rows, const int* kv_indices, const int* kv_indptr, int batch, int heads, int q_len,
+                        int seq_len, int parts, float scale, float kv_scale, int kv_format, void* workspace,
+                        size_t workspace_bytes, void* stream);
 
 /*
  * dst[i] = bf16 bits of src[i] under round_mode, NaN -> 0x7FFF; device pointers.

@@ -31,9 +31,9 @@ def test_abi_version_and_error_strings():
     assert _abi.lib.ma_abi_version() == 1
     m = re.search(r"#define MA_ABI_VERSION (\d+)", open(HEADER).read())
     assert int(m.group(1)) == _abi.ABI_VERSION
-    for rc in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 1001):
+    for rc in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 1001):
         assert _abi.error_string(rc) and "unknown" not in _abi.error_string(rc)
-    assert "unknown" in _abi.error_string(18)
+    assert "unknown" in _abi.error_string(19)
 
 
 def _call(q=16, k=16, v=16, out=16, B=1, H=1, Sq=128, Skv=128, D=128, layout=0, mode=0, ws=0, wsb=0, flags=0):

@@ -1,0 +1,233 @@
+"""GPU tests of the MLA absorbed-decode operators through the C ABI.
+
+The scenarios are those of the reference's tests (tests/test_mla_decode.py:97-221: fp32 reference over the same
+dequantised fp8 KV, rel-L2 < 3e-3, peaked queries, end-aligned causal window, scattered paged pool, `rows`
+remapping, domain errors), checked against oracle/mla_oracle.py; further cases cover what this implementation
+adds or approximates (e4m3 caches, saturated fnuz codes, short and ragged sequences, every q_len, small H).
+"""
+from __future__ import annotations
+
+from itertools import accumulate
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import mla_oracle as mo
+
+pytestmark = pytest.mark.gpu
+
+LAT, ROPE, FUSED = 512, 64, 576
+SCALE = FUSED ** -0.5
+KV_SCALE = 1.0 / 32.0
+QPEAK = 3.0
+REL_L2 = mo.REL_L2
+
+
+@pytest.fixture(scope="module")
+def ma(cuda_device):
+    import moonmath_attention
+
+    return moonmath_attention
+
+
+def _rand_kv(B, S, device, seed, dtype=torch.float8_e4m3fnuz):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(B, S, FUSED, generator=g).to(dtype).to(device)
+
+
+def _rand_q(B, q_len, H, device, seed):
+    g = torch.Generator().manual_seed(seed + 1)
+    shape = (B, H) if q_len is None else (B, q_len, H)
+    q_lat = (torch.randn(*shape, LAT, generator=g) * QPEAK).to(torch.bfloat16).to(device)
+    q_pe = (torch.randn(*shape, ROPE, generator=g) * QPEAK).to(torch.bfloat16).to(device)
+    return q_lat, q_pe, torch.zeros_like(q_lat)
+
+
+def _oracle(q_lat, q_pe, kv, seq_lens, fmt="fnuz"):
+    if q_lat.dim() == 3:
+        q_lat, q_pe = q_lat.unsqueeze(1), q_pe.unsqueeze(1)
+    return mo.mla_decode(q_lat.float().cpu().numpy(), q_pe.float().cpu().numpy(), kv.view(torch.uint8).cpu().numpy(),
+                         seq_lens, SCALE, KV_SCALE, fmt)
+
+
+def _check(ma, o_lat, ref, what=""):
+    out = o_lat.float().cpu().numpy().reshape(ref.shape)
+    assert ma.last_status()[0] == 0, f"{what}: device status {ma.last_status()[:3]}"
+    assert not np.isnan(out).any(), what
+    assert mo.rel_l2(out, ref) < REL_L2, f"{what}: rel-L2 {mo.rel_l2(out, ref):.2e}"
+
+
+def _paged_pool(kv, seq_lens, device, seed):
+    """Scatter the requests' rows over a shared pool in a random permutation of the slots."""
+    total = sum(seq_lens)
+    g = torch.Generator().manual_seed(seed + 2)
+    slots = torch.randperm(total, generator=g).to(torch.int32)
+    pool = torch.zeros(total, 1, FUSED, dtype=torch.uint8)
+    off = 0
+    for b, n in enumerate(seq_lens):
+        pool[slots[off:off + n].long(), 0] = kv[b, :n].cpu().view(torch.uint8)
+        off += n
+    indptr = torch.tensor([0, *accumulate(seq_lens)], dtype=torch.int32)
+    return pool.view(kv.dtype).to(device), slots.to(device), indptr.to(device)
+
+
+# ---- the reference's scenarios ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("H", [12, 16])
+def test_single_query_matches_reference(ma, cuda_device, H):
+    B, S = 2, 2048
+    kv = _rand_kv(B, S, cuda_device, 11)
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 11)
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B), f"q_len 1 H {H}")
+
+
+@pytest.mark.parametrize("q_len", [4, 5, 8])
+@pytest.mark.parametrize("H", [12, 16])
+def test_multiq_contiguous_matches_reference(ma, cuda_device, q_len, H):
+    B, S = 2, 2048
+    kv = _rand_kv(B, S, cuda_device, 23)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 23)
+    ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B), f"multiq {q_len} H {H}")
+
+
+def test_multiq_causal_window_is_end_aligned(ma, cuda_device):
+    """Poisoning the last q_len - 1 rows moves the last draft position and leaves the first bit-identical."""
+    B, S, H, q_len = 1, 2048, 16, 4
+    kv = _rand_kv(B, S, cuda_device, 31)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 31)
+    ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    base = o_lat.clone()
+    kv[:, S - q_len + 1:] = _rand_kv(B, q_len - 1, cuda_device, 99)
+    ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    assert torch.equal(o_lat[:, 0], base[:, 0]), "position 0 read past its causal limit"
+    assert not torch.equal(o_lat[:, -1], base[:, -1]), "last position missed the tail tokens"
+
+
+@pytest.mark.parametrize("q_len", [4, 8])
+def test_multiq_paged_matches_reference(ma, cuda_device, q_len):
+    B, H = 3, 16
+    seq_lens = [2048, 2064, 1024]
+    S = max(seq_lens)
+    kv = _rand_kv(B, S, cuda_device, 43)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 43)
+    pool, kv_indices, kv_indptr = _paged_pool(kv, seq_lens, cuda_device, 43)
+    lens = torch.tensor(seq_lens, dtype=torch.int32, device=cuda_device)
+    parts = ma.mla_decode_a16w8_multiq_plan_parts_q(B, S, q_len, H)
+    assert parts >= 1
+    ma.mla_decode_a16w8_multiq_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, seq_lens), f"paged multiq {q_len}")
+
+
+def test_multiq_paged_rows_remaps_query_and_output(ma, cuda_device):
+    B, H, q_len = 4, 16, 4
+    seq_lens = [2048] * B
+    kv = _rand_kv(B, seq_lens[0], cuda_device, 57)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 57)
+    pool, kv_indices, kv_indptr = _paged_pool(kv, seq_lens, cuda_device, 57)
+    lens = torch.tensor(seq_lens, dtype=torch.int32, device=cuda_device)
+    parts = ma.mla_decode_a16w8_multiq_plan_parts_q(B, seq_lens[0], q_len, H)
+    ma.mla_decode_a16w8_multiq_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    identity = o_lat.clone()
+    rows = torch.arange(B - 1, -1, -1, dtype=torch.int32, device=cuda_device)
+    o_rev = torch.zeros_like(o_lat)
+    ma.mla_decode_a16w8_multiq_paged_dev(q_lat.flip(0).contiguous(), q_pe.flip(0).contiguous(), pool, o_rev, lens, rows,
+                                         kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    assert torch.equal(o_rev.flip(0), identity)
+
+
+@pytest.mark.parametrize("q_len", [1, 3, 9])
+def test_multiq_rejects_q_len_out_of_domain(ma, cuda_device, q_len):
+    kv = _rand_kv(1, 256, cuda_device, 71)
+    q_lat, q_pe, o_lat = _rand_q(1, q_len, 16, cuda_device, 71)
+    with pytest.raises(ValueError, match="q_len"):
+        ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+
+
+def test_multiq_rejects_too_many_heads(ma, cuda_device):
+    kv = _rand_kv(1, 256, cuda_device, 73)
+    q_lat, q_pe, o_lat = _rand_q(1, 4, 17, cuda_device, 73)
+    with pytest.raises(ValueError, match="H must be"):
+        ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+
+
+def test_multiq_rejects_q_len_1_rank(ma, cuda_device):
+    kv = _rand_kv(1, 256, cuda_device, 79)
+    q_lat, q_pe, o_lat = _rand_q(1, None, 16, cuda_device, 79)
+    with pytest.raises(ValueError, match=r"\[B,q_len,H,512\]"):
+        ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+
+
+# ---- beyond the reference's tests ------------------------------------------------------------------------------
+@pytest.mark.parametrize("B,H,S", [(1, 16, 1), (1, 1, 127), (3, 5, 129), (2, 16, 1000), (5, 7, 4097)])
+def test_single_query_ragged_lengths_and_few_heads(ma, cuda_device, B, H, S):
+    kv = _rand_kv(B, S, cuda_device, 5)
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 5)
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B), f"B {B} H {H} S {S}")
+
+
+@pytest.mark.parametrize("q_len", [1, 2, 3, 6, 7])
+@pytest.mark.parametrize("parts", [1, 3, 64])
+def test_paged_every_window_length_and_split(ma, cuda_device, q_len, parts):
+    B, H = 2, 16
+    seq_lens = [700, 1301]
+    kv = _rand_kv(B, max(seq_lens), cuda_device, 17)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len if q_len > 1 else None, H, cuda_device, 17)
+    pool, kv_indices, kv_indptr = _paged_pool(kv, seq_lens, cuda_device, 17)
+    lens = torch.tensor(seq_lens, dtype=torch.int32, device=cuda_device)
+    ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, seq_lens), f"paged q_len {q_len} parts {parts}")
+
+
+def test_e4m3_cache_is_read_unchanged(ma, cuda_device):
+    B, S, H = 2, 1500, 16
+    kv = _rand_kv(B, S, cuda_device, 29, torch.float8_e4m3fn)
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 29)
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B, "fn"), "e4m3fn cache")
+
+
+def test_saturated_fnuz_codes_do_not_turn_into_nan(ma, cuda_device):
+    """0x7F / 0xFF are +-240 in e4m3-fnuz and NaN in the format the tensor core reads; the kernel rewrites them
+    to +-224.  With one entry in a hundred saturated the result stays finite and close to the exact one."""
+    B, S, H = 1, 1024, 16
+    kv = _rand_kv(B, S, cuda_device, 37)
+    raw = kv.view(torch.uint8)
+    g = torch.Generator().manual_seed(3)
+    hit = (torch.rand(raw.shape, generator=g) < 0.01).to(cuda_device)
+    sign = (torch.rand(raw.shape, generator=g) < 0.5).to(cuda_device)
+    raw[hit & sign] = 0x7F
+    raw[hit & ~sign] = 0xFF
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 37)
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, 1.0 / 512.0)  # a scale that keeps the softmax spread out
+    out = o_lat.float().cpu().numpy()
+    assert ma.last_status()[0] == 0 and np.isfinite(out).all()
+    qa, qb = q_lat.unsqueeze(1).float().cpu().numpy(), q_pe.unsqueeze(1).float().cpu().numpy()
+    # the documented behaviour, exactly: the same cache with the two codes moved one down
+    moved = raw.cpu().numpy().copy()
+    moved[moved == 0x7F] = 0x7E
+    moved[moved == 0xFF] = 0xFE
+    assert mo.rel_l2(out.reshape(1, 1, H, LAT), mo.mla_decode(qa, qb, moved, [S], SCALE, 1.0 / 512.0)) < REL_L2
+    # ... and how far that is from the true values when one entry in a hundred is saturated (240 -> 224 is 6.7 %)
+    assert mo.rel_l2(out.reshape(1, 1, H, LAT), mo.mla_decode(qa, qb, raw.cpu().numpy(), [S], SCALE, 1.0 / 512.0)) < 0.1
+
+
+def test_contiguous_argument_errors(ma, cuda_device):
+    kv = _rand_kv(2, 256, cuda_device, 83)
+    q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
+    with pytest.raises(ValueError, match="float8_e4m3fnuz"):
+        ma.mla_decode_a16w8(q_lat, q_pe, kv.view(torch.uint8), o_lat, SCALE, KV_SCALE)
+    with pytest.raises(ValueError, match="FUSED"):
+        ma.mla_decode_a16w8(q_lat, q_pe, kv[..., :512].contiguous(), o_lat, SCALE, KV_SCALE)
+    with pytest.raises(ValueError, match="batch"):
+        ma.mla_decode_a16w8(q_lat, q_pe, kv[:1], o_lat, SCALE, KV_SCALE)
+    with pytest.raises(ValueError, match="bfloat16"):
+        ma.mla_decode_a16w8(q_lat.float(), q_pe, kv, o_lat, SCALE, KV_SCALE)
+    with pytest.raises(ValueError, match="q_len==1 only"):
+        q4 = _rand_q(2, 4, 16, cuda_device, 83)
+        ma.mla_decode_a16w8(q4[0], q4[1], kv, q4[2], SCALE, KV_SCALE)
+    lens = torch.tensor([256, 256], dtype=torch.int64, device=cuda_device)
+    with pytest.raises(ValueError, match="int32"):
+        ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, kv.view(512, 1, FUSED), o_lat, lens, None, lens, lens, 1, SCALE, KV_SCALE)

@@ -1,0 +1,72 @@
+"""CPU tests of the MLA oracle's cache-format tables, the planner and the argument checks of the C ABI."""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+import torch
+
+from moonmath_attention import _abi
+from oracle import mla_oracle as mo
+
+
+def test_fp8_tables_match_torch_for_every_code():
+    codes = torch.arange(256, dtype=torch.uint8)
+    for name, table, dt in (("fnuz", mo.decode_e4m3fnuz(), torch.float8_e4m3fnuz), ("fn", mo.decode_e4m3fn(), torch.float8_e4m3fn)):
+        want = codes.view(dt).float().numpy()
+        assert np.array_equal(np.isnan(table), np.isnan(want)), name
+        ok = ~np.isnan(want)
+        assert np.array_equal(table[ok], want[ok]), name
+
+
+def test_fnuz_bytes_read_as_e4m3_are_twice_their_value():
+    # what the kernel relies on: every finite code but the two the tensor-core format reserves for NaN
+    fnuz, fn = mo.decode_e4m3fnuz(), mo.decode_e4m3fn()
+    for b in range(256):
+        if b in (0x80, 0x7F, 0xFF):
+            continue
+        assert fn[b] == 2 * fnuz[b], hex(b)
+    assert fnuz[0x7F] == 240 and fnuz[0xFF] == -240 and fnuz[0x7E] == 224 and np.isnan(fnuz[0x80])
+
+
+def test_oracle_is_the_softmax_formula_of_the_reference_test():
+    rng = np.random.default_rng(3)
+    B, q_len, H, S = 2, 3, 4, 40
+    kv = torch.randn(B, S, mo.FUSED, generator=torch.Generator().manual_seed(1)).to(torch.float8_e4m3fnuz)
+    q_lat = rng.standard_normal((B, q_len, H, 512)).astype(np.float32)
+    q_pe = rng.standard_normal((B, q_len, H, 64)).astype(np.float32)
+    out = mo.mla_decode(q_lat, q_pe, kv.view(torch.uint8).numpy(), [S, S - 5], 576 ** -0.5, 1 / 32)
+    k = kv.float() / 32
+    for b, slen in enumerate([S, S - 5]):
+        for t in range(q_len):
+            end = slen - q_len + t + 1
+            score = (torch.from_numpy(q_lat[b, t]) @ k[b, :end, :512].T + torch.from_numpy(q_pe[b, t]) @ k[b, :end, 512:].T) * 576 ** -0.5
+            want = torch.softmax(score, dim=-1) @ k[b, :end, :512]
+            np.testing.assert_allclose(out[b, t], want.numpy(), rtol=2e-5, atol=1e-6)
+
+
+def test_planner_fills_the_gpu_once_and_keeps_parts_long():
+    plan = lambda B, q, S: _abi.lib.ma_mla_plan_parts(B, q, S, 148)
+    assert plan(148, 1, 4096) == 1 and plan(300, 1, 4096) == 1
+    assert plan(32, 1, 8192) == 4                # 148 // 32, 16 parts of four tiles available
+    assert plan(16, 4, 8192) == 2                # a window of four positions is four CTAs per part
+    assert plan(1, 1, 131072) == 64              # capped by MA_MLA_MAX_PARTS
+    assert plan(1, 1, 1000) == 2                 # 8 tiles: at least four tiles per part
+    assert plan(1, 1, 100) == 1
+    assert plan(0, 1, 100) == 1 and plan(1, 9, 100) == 1
+    ws = _abi.lib.ma_mla_workspace_bytes
+    assert ws(32, 1, 4) == 256 + 32 * 4 * 16 * 514 * 4
+    assert ws(2, 8, 3) == 256 + 2 * 8 * 3 * 16 * 514 * 4
+
+
+def test_mla_argument_validation_return_codes():
+    def call(B=1, H=16, q_len=1, S=128, parts=1, fmt=0, q=16, idx=None, indptr=None, lens=None, ws=0, wsb=0):
+        return _abi.lib.ma_mla_decode_a16w8(q, 16, 16, 16, lens, None, idx, indptr, B, H, q_len, S, parts,
+                                            ctypes.c_float(0.04), ctypes.c_float(1.0), fmt, ws, wsb, None)
+    assert call(B=0) == 1 and call(H=17) == 1 and call(H=0) == 1
+    assert call(q_len=0) == 2 and call(q_len=9) == 2
+    assert call(S=0) == 5 and call(idx=16) == 5          # paged needs kv_indptr and seq_lens
+    assert call(parts=0) == 18 and call(parts=65) == 18 and call(fmt=2) == 18
+    assert call(q=None) == 9 and call(q=8) == 10
+    assert call() == 11                                    # workspace is required
+    assert b"parts" in _abi.lib.ma_error_string(18)
