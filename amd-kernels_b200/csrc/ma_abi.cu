@@ -2,6 +2,7 @@
 // checks, tensor maps, tail plan, kernel launches.  Keeps no state between
 // calls apart from the lazily resolved driver entry point.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -48,6 +49,21 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int 
   }
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, elem,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? MA_OK : MA_ERR_TENSOR_MAP;
+}
+
+// Rank-3 byte map over a contiguous MLA cache slab [batch][seq][576]: box = one 128-byte column chunk of 96 token
+// rows; rows past `seq` and bytes past 576 read as zeros.
+int make_kv_slab_map(CUtensorMap* tm, const void* ptr, int batch, int seq) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return MA_ERR_DRIVER;
+  const cuuint64_t dims[3] = {576, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {576, static_cast<cuuint64_t>(576) * seq};
+  const cuuint32_t box[3] = {128, 96, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, elem,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MA_OK : MA_ERR_TENSOR_MAP;
@@ -344,6 +360,8 @@ namespace {
 // csrc/mla_decode_a16w8.hip "QLC=1").  The kernel template also takes two, but its softmax then keeps twice
 // the per-row state in registers and measured slower.
 int mla_pos_per_cta(int) { return 1; }
+// Development switch: MA_MLA_NO_TMA=1 sends a contiguous slab through the copy path of the paged pool.
+bool flags_env_no_tma() { return std::getenv("MA_MLA_NO_TMA") != nullptr; }
 int mla_groups(int q_len) { return (q_len + mla_pos_per_cta(q_len) - 1) / mla_pos_per_cta(q_len); }
 }  // namespace
 
@@ -397,6 +415,11 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
   p.batch = batch, p.heads = heads, p.q_len = q_len, p.seq = seq_len;
   p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len), p.groups = mla_groups(q_len);
   p.kv_format = kv_format, p.scale = scale, p.kv_scale = kv_scale;
+  if (!paged && !(flags_env_no_tma())) {
+    const int rc = make_kv_slab_map(&p.tm_kv, kv, batch, seq_len);
+    if (rc != MA_OK) return rc;
+    p.use_tma = 1;
+  }
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   p.status = reinterpret_cast<uint32_t*>(ws);
   const size_t slots = static_cast<size_t>(batch) * p.groups * parts, r = 16u * p.pos_per_cta;

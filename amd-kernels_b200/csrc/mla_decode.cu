@@ -7,9 +7,9 @@
 // with kv stored as fp8 rows of 576 bytes at one per-tensor scale, contiguous or paged one token per slot.
 //
 // How: the KV bytes go to the tensor core as they are.  The reference unpacks fp8 to bf16 on the way into
-// LDS; here a tile of 128 tokens x 576 bytes is the A operand of fp8 MMAs (kind::f8f6f4) twice:
-//   S^T[128 tokens x N]   = KV[128 x 576] (K-major)  x  Q^T[576 x N]
-//   O^T[4 x 128 dims x N] = KV^T (same bytes, MN-major, 128 latent bytes of a row per M tile)  x  P^T[128 tokens x N]
+// LDS; here a tile of 96 tokens x 576 bytes is the A operand of fp8 MMAs (kind::f8f6f4) twice:
+//   S^T[tokens x N]       = KV[96 x 576] (K-major)  x  Q^T[576 x N]
+//   O^T[4 x 128 dims x N] = KV^T (same bytes, MN-major, 128 latent bytes of a row per M tile)  x  P^T[96 tokens x N]
 // The 16-bit operands become sums of two e4m3 terms, stacked along N (N = 2 x rows): a query row scaled by a
 // power of two splits exactly into q1 + q2 (8 significant bits = 4 + 4); a probability splits the same
 // way (the reference rounds it to bf16, also 8 bits).  The terms' partial sums sit in separate accumulator
@@ -35,11 +35,12 @@ namespace {
 using namespace sm100;
 
 constexpr int kLat = 512, kRowBytes = 576;
-constexpr int kTok = 128;                        // tokens per tile
+constexpr int kTok = 96;                         // tokens per tile
+constexpr int kMmaM = 128;                       // rows of an MMA; S^T rows 96..127 are never looked at (see role_mma)
 constexpr int kChunks = 5;                       // 128-byte column chunks of a row: 4 latent + rope (64 bytes used)
-constexpr int kChunkBytes = kTok * 128;          // 16 KiB
+constexpr int kChunkBytes = kTok * 128;          // 12 KiB
 constexpr int kTileBytesMla = kChunks * kChunkBytes;
-constexpr int kStagesMla = 2;
+constexpr int kStagesMla = 3;                    // a tile spends about as long being loaded and checked as being used
 constexpr int kHeadsMax = 16;
 constexpr int kSoftmaxThreads = 128, kCopyThreads = 256, kCheckThreads = 128;
 constexpr int kThreadsMla = kSoftmaxThreads + 32 + kCopyThreads + kCheckThreads;  // 544
@@ -60,16 +61,16 @@ struct Cfg {
   static constexpr uint32_t kOffBars = kOffFlags + 2 * 4 * 4;
 };
 enum MlaBar : uint32_t {
-  kMTileFull = 0,   // [2] check warps -> MMA (128 arrivals)
-  kMTileEmpty = 2,  // [2] MMA -> loaders
-  kMSFull = 4,      // [2] MMA -> softmax
-  kMPFull = 6,      // [2] softmax -> MMA (128 arrivals)
-  kMPvDone = 8,     // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
-  kMMx = 10,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
-  kMFlag = 12,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
-  kMEpi = 14,       //     softmax warps among themselves: denominators written (4 arrivals)
-  kMTileRaw = 15,   // [2] copy warps -> check warps: the tile's copies have landed (128 arrivals)
-  kMNumBars = 17
+  kMTileFull = 0,   // [3] check warps -> MMA (128 arrivals)
+  kMTileEmpty = 3,  // [3] MMA -> copy warps
+  kMTileRaw = 6,    // [3] copy warps -> check warps: the tile has landed (256 copy threads, or 1 + bytes for box loads)
+  kMSFull = 9,      // [2] MMA -> softmax
+  kMPFull = 11,     // [2] softmax -> MMA (128 arrivals)
+  kMPvDone = 13,    // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
+  kMMx = 15,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
+  kMFlag = 17,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
+  kMEpi = 19,       //     softmax warps among themselves: denominators written (4 arrivals)
+  kMNumBars = 20
 };
 
 #ifdef MA_TRACE
@@ -168,17 +169,37 @@ template <int kPos>
 __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uint32_t base, int lt, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
   const uint32_t bars = base + C::kOffBars;
+  if (p.use_tma) {
+    // Contiguous slab: five box loads per tile (one per 128-byte column chunk, 96 rows each), issued by one
+    // thread.  Rows past the slab and the columns past byte 576 of the rope chunk arrive as zeros.
+    if (lt != 0) return;
+    for (int j = 0; j < w.tiles; ++j) {
+      const int st = j % kStagesMla;
+      if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / kStagesMla) - 1) & 1, 0x50);
+      MLA_TRACE_AT(4000 + j * 4 + 0, j < 60);
+      const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
+      const uint32_t bar = bars + 8 * (kMTileRaw + st);
+      mbar_arrive_expect_tx(bar, kTileBytesMla);
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) tma_load_3d(tile + c * kChunkBytes, &p.tm_kv, bar, c * 128, (w.tile0 + j) * kTok, w.b);
+      MLA_TRACE_AT(4000 + j * 4 + 1, j < 60);
+    }
+    return;
+  }
   const uint8_t* kv = static_cast<const uint8_t*>(p.kv);
   const int idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
-  constexpr int kPerThread = kTok * (kRowBytes / 16) / kCopyThreads;  // 18 copies per tile
+  constexpr int kPieces = kTok * (kRowBytes / 16);                        // 3456 copies of 16 bytes per tile
+  constexpr int kPerThread = (kPieces + kCopyThreads - 1) / kCopyThreads;  // 14 (the last one for half the threads)
   for (int j = 0; j < w.tiles; ++j) {
-    if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + (j & 1)), ((j >> 1) - 1) & 1, 0x50);
+    const int st = j % kStagesMla;
+    if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / kStagesMla) - 1) & 1, 0x50);
     MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
-    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
     const int tok0 = (w.tile0 + j) * kTok;
 #pragma unroll
     for (int i = 0; i < kPerThread; ++i) {
       const int id = i * kCopyThreads + lt;
+      if (id >= kPieces) break;
       const int tok = id / 36, q = id % 36;
       const int tok_abs = tok0 + tok;
       const bool live = tok_abs < w.end_max;  // rows past the end are zero-filled (source size 0)
@@ -188,7 +209,7 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
       const uint32_t col = static_cast<uint32_t>(q) * 16u;
       cp_async16(tile + (col >> 7) * kChunkBytes + swz128(tok, col & 127u), kv + slot * kRowBytes + col, live ? 16u : 0u);
     }
-    cp_async_arrive(bars + 8 * (kMTileRaw + (j & 1)));
+    cp_async_arrive(bars + 8 * (kMTileRaw + st));
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
   }
 }
@@ -199,16 +220,17 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
   using C = Cfg<kPos>;
   const uint32_t bars = base + C::kOffBars;
   const bool fnuz = p.kv_format == 0;
-  constexpr int kPerThread = kTileBytesMla / 16 / kCheckThreads;  // 40 x 16 bytes per tile (the rope chunk's unused half included)
+  constexpr int kPerThread = kTileBytesMla / 16 / kCheckThreads;  // 30 x 16 bytes per tile (the rope chunk's unused half included)
   for (int j = 0; j < w.tiles; ++j) {
-    MA_WAIT_SLEEP(32, bars + 8 * (kMTileRaw + (j & 1)), (j >> 1) & 1, 0x58);
+    const int st = j % kStagesMla;
+    MA_WAIT_SLEEP(32, bars + 8 * (kMTileRaw + st), (j / kStagesMla) & 1, 0x58);
     MLA_TRACE_AT(4000 + j * 4 + 2, lt == 0 && j < 60);
+    uint4* tile = reinterpret_cast<uint4*>(smem + C::kOffKV + st * kTileBytesMla);
     if (fnuz) {
       // 0x7F / 0xFF (+-240 in e4m3-fnuz) are NaN to the tensor core: one code down (+-224).  First pass: is any
       // such byte among this thread's share?  (Hardly ever.)  Only then a second pass rewrites.
-      uint4* tile = reinterpret_cast<uint4*>(smem + C::kOffKV + (j & 1) * kTileBytesMla);
       uint32_t any = 0;
-#pragma unroll 8
+#pragma unroll 10
       for (int i = 0; i < kPerThread; ++i) {
         const uint4 v = tile[i * kCheckThreads + lt];
         any |= ((v.x & 0x7F7F7F7Fu) + 0x01010101u) | ((v.y & 0x7F7F7F7Fu) + 0x01010101u) |
@@ -223,9 +245,19 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
           tile[i * kCheckThreads + lt] = v;
         }
       }
+    } else if (p.use_tma) {
+      // An e4m3 cache keeps its NaN codes.  Box loads bring whole rows, also those between the end of the
+      // request and the end of the slab, which nobody wrote for this request: zero them (P = 0 meets them).
+      const int live_rows = w.end_max - (w.tile0 + j) * kTok;
+      if (live_rows < kTok) {
+        for (int i = lt; i < kTileBytesMla / 16; i += kCheckThreads) {
+          const int row = (i % (kChunkBytes / 16)) / 8;  // 8 pieces of 16 bytes per row and chunk
+          if (row >= live_rows) tile[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
     }
     fence_proxy_async_smem();
-    mbar_arrive(bars + 8 * (kMTileFull + (j & 1)));
+    mbar_arrive(bars + 8 * (kMTileFull + st));
     MLA_TRACE_AT(4000 + j * 4 + 3, lt == 0 && j < 60);
   }
 }
@@ -237,13 +269,19 @@ template <int kPos>
 __device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
   constexpr uint32_t kFmtE4M3 = 0;
-  constexpr uint32_t idesc_qk = umma_idesc(kFmtE4M3, kFmtE4M3, 0, 0, kTok, C::kN);
-  constexpr uint32_t idesc_pv = umma_idesc(kFmtE4M3, kFmtE4M3, 1, 0, kTok, C::kN);
+  constexpr uint32_t idesc_qk = umma_idesc(kFmtE4M3, kFmtE4M3, 0, 0, kMmaM, C::kN);
+  constexpr uint32_t idesc_pv = umma_idesc(kFmtE4M3, kFmtE4M3, 1, 0, kMmaM, C::kN);
   const uint32_t bars = base + C::kOffBars;
   const uint32_t qt_lo = desc_lo_kmajor(base + C::kOffQT);
   const int n = w.tiles;
+  // Q K^T runs with M = 128 over chunks of 96 token rows: rows 96..127 of the A operand are the first 32 rows
+  // of whatever follows the chunk in shared memory.  A row of D depends on its own row of A only, so this
+  // fills S^T rows 96..127 with numbers nobody reads.  P V has the tokens on K: three steps of 32, exact.
+  // Q K^T runs with M = 128 over chunks of 96 token rows: rows 96..127 of the A operand are the first 32 rows
+  // of whatever follows the chunk in shared memory.  A row of D depends on its own row of A only, so this
+  // fills S^T rows 96..127 with numbers nobody reads.  P V has the tokens on K: three steps of 32, exact.
   auto issue_qk = [&](int j) {
-    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
     const uint32_t a_lo = desc_lo_kmajor(tile);
     const uint32_t d = tmem + (j & 1) * C::kN;
 #pragma unroll
@@ -257,19 +295,19 @@ __device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t 
     umma_commit(bars + 8 * (kMSFull + (j & 1)));
   };
   auto issue_pv = [&](int j) {
-    const uint32_t tile = base + C::kOffKV + (j & 1) * kTileBytesMla;
+    const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
     const uint32_t pt_lo = desc_lo_kmajor(base + C::kOffPT + (j & 1) * C::kN * 128);
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) {
       // A = 128 latent bytes of every token row (M), 32 token rows per step (K): MN-major, one swizzle atom wide
       const uint32_t a_lo = desc_lo_mnmajor<kTok>(tile + mt * kChunkBytes);
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
+      for (int ks = 0; ks < kTok / 32; ++ks) {
         umma_ss_f8(tmem + (2 + mt) * C::kN, make_desc(a_lo + ((ks * 32 * 128) >> 4)), make_desc(pt_lo + ((ks * 32) >> 4)),
                    idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
       }
     }
-    umma_commit(bars + 8 * (kMTileEmpty + (j & 1)));
+    umma_commit(bars + 8 * (kMTileEmpty + (j % kStagesMla)));
     umma_commit(bars + 8 * (kMPvDone + (j & 1)));
   };
   // Whatever is ready is issued: Q K^T of tile i needs the tile and the S buffer (read out by the softmax of
@@ -279,7 +317,8 @@ __device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t 
   uint64_t t0 = 0;
   while (pv_i < n) {
     bool progressed = false;
-    if (qk_i < n && qk_i - pv_i < 2 && mbar_test_wait(bars + 8 * (kMTileFull + (qk_i & 1)), (qk_i >> 1) & 1)) {
+    if (qk_i < n && qk_i - pv_i < 2 &&
+        mbar_test_wait(bars + 8 * (kMTileFull + (qk_i % kStagesMla)), (qk_i / kStagesMla) & 1)) {
       tc_fence_after_sync();
       MLA_TRACE_AT(2000 + qk_i * 8 + 1, qk_i < 60);
       issue_qk(qk_i);
@@ -377,7 +416,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       // position (r / 16) of the group sees tokens [0, len - q_len + pos + 1)
       const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
       const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * row_scale[r];
-      s[r] = tok_abs < limit ? v : -INFINITY;
+      s[r] = (tl < kTok && tok_abs < limit) ? v : -INFINITY;
       over = fmaxf(over, s[r] - m_ref[r]);
     }
     const bool warp_over = __any_sync(0xffffffffu, over > kTauMla) || j == 0;
@@ -452,12 +491,14 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     if (j >= 2) MA_WAIT_WARP(bars + 8 * (kMPvDone + buf), ((j - 2) >> 1) & 1, 0x73);
     MLA_TRACE_AT(j * 8 + 5, tr);
     uint8_t* pt = smem + C::kOffPT + buf * N * 128;
+    if (tl < kTok) {
 #pragma unroll
     for (int r = 0; r < R; r += 2) {
       pt[swz128(r, tl)] = static_cast<uint8_t>(t1[r / 2] & 0xFF);
       pt[swz128(r + 1, tl)] = static_cast<uint8_t>(t1[r / 2] >> 8);
       pt[swz128(R + r, tl)] = static_cast<uint8_t>(t2[r / 2] & 0xFF);
       pt[swz128(R + r + 1, tl)] = static_cast<uint8_t>(t2[r / 2] >> 8);
+    }
     }
     fence_proxy_async_smem();
     tc_fence_before_sync();
@@ -523,8 +564,8 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
     const uint32_t bars = base + C::kOffBars;
     for (uint32_t i = 0; i < kMNumBars; ++i) {
       uint32_t count = 1;
-      if (i >= kMTileFull && i < kMTileFull + 2) count = kCheckThreads;
-      if (i >= kMTileRaw && i < kMTileRaw + 2) count = kCopyThreads;
+      if (i >= kMTileFull && i < kMTileFull + kStagesMla) count = kCheckThreads;
+      if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = p.use_tma ? 1u : static_cast<uint32_t>(kCopyThreads);
       if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
       if (i >= kMMx && i <= kMEpi) count = 4;
       mbar_init(bars + 8 * i, count);
