@@ -186,28 +186,39 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     }
     return;
   }
+  // Paged pool (or a slab sent this way): a warp copies 12 whole token rows of the tile, 36 pieces of 16 bytes
+  // each.  Lane k < 12 holds the pool slot of the warp's k-th row, fetched one tile ahead, so that no copy
+  // waits for an index load of its own.
   const uint8_t* kv = static_cast<const uint8_t*>(p.kv);
   const int idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
-  constexpr int kPieces = kTok * (kRowBytes / 16);                        // 3456 copies of 16 bytes per tile
-  constexpr int kPerThread = (kPieces + kCopyThreads - 1) / kCopyThreads;  // 14 (the last one for half the threads)
+  const int warp = lt >> 5, lane = lt & 31;
+  constexpr int kRowsPerWarp = kTok / (kCopyThreads / 32);  // 12
+  constexpr int kPiecesPerWarp = kRowsPerWarp * 36;         // 432 = 13.5 warp-wide copies
+  auto slot_of = [&](int j) -> long long {  // slot of row `lane` of this warp in tile j; -1: past the end
+    const int tok_abs = (w.tile0 + j) * kTok + warp * kRowsPerWarp + lane;
+    if (lane >= kRowsPerWarp || j >= w.tiles || tok_abs >= w.end_max) return -1;
+    return p.kv_indices != nullptr ? static_cast<long long>(p.kv_indices[idx0 + tok_abs])
+                                   : static_cast<long long>(w.b) * p.seq + tok_abs;
+  };
+  long long slot_next = slot_of(0);
   for (int j = 0; j < w.tiles; ++j) {
     const int st = j % kStagesMla;
+    const long long slot_mine = slot_next;
+    slot_next = slot_of(j + 1);
     if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / kStagesMla) - 1) & 1, 0x50);
     MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
     const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
-    const int tok0 = (w.tile0 + j) * kTok;
 #pragma unroll
-    for (int i = 0; i < kPerThread; ++i) {
-      const int id = i * kCopyThreads + lt;
-      if (id >= kPieces) break;
-      const int tok = id / 36, q = id % 36;
-      const int tok_abs = tok0 + tok;
-      const bool live = tok_abs < w.end_max;  // rows past the end are zero-filled (source size 0)
-      const size_t slot = !live ? 0
-                          : p.kv_indices != nullptr ? static_cast<size_t>(p.kv_indices[idx0 + tok_abs])
-                                                    : static_cast<size_t>(w.b) * p.seq + tok_abs;
-      const uint32_t col = static_cast<uint32_t>(q) * 16u;
-      cp_async16(tile + (col >> 7) * kChunkBytes + swz128(tok, col & 127u), kv + slot * kRowBytes + col, live ? 16u : 0u);
+    for (int i = 0; i < (kPiecesPerWarp + 31) / 32; ++i) {
+      const int piece = i * 32 + lane;
+      const int row = piece / 36, q = piece % 36;  // row 12 only in the last, half-empty round
+      const long long slot = __shfl_sync(0xffffffffu, slot_mine, row < kRowsPerWarp ? row : 0);
+      if (piece < kPiecesPerWarp) {
+        const uint32_t tok = warp * kRowsPerWarp + row, col = static_cast<uint32_t>(q) * 16u;
+        // rows past the end are zero-filled (source size 0)
+        cp_async16(tile + (col >> 7) * kChunkBytes + swz128(tok, col & 127u),
+                   kv + (slot < 0 ? 0 : slot) * kRowBytes + col, slot < 0 ? 0u : 16u);
+      }
     }
     cp_async_arrive(bars + 8 * (kMTileRaw + st));
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
