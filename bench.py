@@ -42,7 +42,7 @@ WORKLOADS = {
 PUBLISHED_TFLOPS = {"rtne": 535.0, "rtna": 545.8, "rtz": 552.9}
 # dram__bytes_read.sum + dram__bytes_write.sum of one attn_pipelined_kernel launch at the c2 shape
 # (profiles/ncu_attn_pipelined_c2.md).
-NCU_TRAFFIC_BYTES = {"c2": 302455040 + 87395072}
+NCU_TRAFFIC_BYTES = {"c2": 302978048 + 87565824}
 
 
 def measured_peaks() -> tuple[float, float, str]:
