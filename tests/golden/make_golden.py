@@ -34,7 +34,9 @@ ROWS = [0, 1, 2, 63, 64, 127, 128, 255, 256, 511, 640, 777, 1000, 1022, 1023]
 
 
 def main() -> None:
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of the reference repository>")
+    ref_root = Path(sys.argv[1])
     script = ref_root / "examples" / "basic.py"
     stub = types.ModuleType("moonmath_attention")
     stub.forward = lambda q, k, v, **kw: torch.zeros_like(q)
