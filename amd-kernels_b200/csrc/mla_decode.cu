@@ -17,9 +17,11 @@
 // owns one token (softmax) or one output dimension (rescale, epilogue).
 //
 // e4m3-fnuz (the reference's format) differs from the e4m3 the tensor core reads by a factor of two in
-// every finite value, folded into the scales, and in two codes: 0x7F / 0xFF are +-240 there and NaN here,
-// so the loader rewrites them to 0x7E / 0xFE (+-224: the one approximation of this kernel, on saturated
-// cache entries only); 0x80 (NaN there) reads as zero.  e4m3 caches (kv_format 1) are read unchanged.
+// every finite value, folded into the scales, and in two codes: 0x7F / 0xFF are +-240 there and NaN here.
+// The check warps rewrite them to 0x7E / 0xFE (+-224) and list them; the softmax warps add the missing
+// +-16 x q to the scores and +-16 x p to the outputs by hand, so the result is exact for up to 640 such
+// entries per tile of 96 tokens (beyond that the rest stay at +-224).  0x80 (NaN there) reads as zero.
+// e4m3 caches (kv_format 1) are read unchanged.
 //
 // One CTA per (request, group of draft positions, KV part); parts are merged by mla_merge_kernel.
 //   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12  copy    warps 13-16  check
@@ -45,6 +47,8 @@ constexpr int kHeadsMax = 16;
 constexpr int kSoftmaxThreads = 128, kCopyThreads = 256, kCheckThreads = 128;
 constexpr int kThreadsMla = kSoftmaxThreads + 32 + kCopyThreads + kCheckThreads;  // 544
 constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
+constexpr int kSatCap = 640;                     // saturated e4m3-fnuz entries of one tile that are corrected exactly
+constexpr float kSatResidual = 32.f;             // +-240 fnuz = +-480 as e4m3; the tensor core gets +-448; the rest by hand
 
 template <int kPos>
 struct Cfg {
@@ -58,7 +62,9 @@ struct Cfg {
   static constexpr uint32_t kOffMx = kOffRowScale + kRows * 4;         // float [2][4 warps][kRows]
   static constexpr uint32_t kOffL = kOffMx + 2 * 4 * kRows * 4;        // float [4 warps][kRows]: denominators (epilogue)
   static constexpr uint32_t kOffFlags = kOffL + 4 * kRows * 4;         // int [2][4 warps]
-  static constexpr uint32_t kOffBars = kOffFlags + 2 * 4 * 4;
+  static constexpr uint32_t kOffSatCnt = kOffFlags + 2 * 4 * 4;        // int [kStagesMla]: saturated entries of the tile in a stage; [3]: first P V accumulates
+  static constexpr uint32_t kOffSat = kOffSatCnt + 16;                 // uint32 [kStagesMla][kSatCap]: token | column << 7 | negative << 17
+  static constexpr uint32_t kOffBars = kOffSat + kStagesMla * kSatCap * 4;
 };
 enum MlaBar : uint32_t {
   kMTileFull = 0,   // [3] check warps -> MMA (128 arrivals)
@@ -70,7 +76,8 @@ enum MlaBar : uint32_t {
   kMMx = 15,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
   kMFlag = 17,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
   kMEpi = 19,       //     softmax warps among themselves: denominators written (4 arrivals)
-  kMNumBars = 20
+  kMSat = 20,       // [2] softmax warps among themselves: P^T written, before a saturation correction (4 arrivals)
+  kMNumBars = 22
 };
 
 #ifdef MA_TRACE
@@ -238,8 +245,9 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
     MLA_TRACE_AT(4000 + j * 4 + 2, lt == 0 && j < 60);
     uint4* tile = reinterpret_cast<uint4*>(smem + C::kOffKV + st * kTileBytesMla);
     if (fnuz) {
-      // 0x7F / 0xFF (+-240 in e4m3-fnuz) are NaN to the tensor core: one code down (+-224).  First pass: is any
-      // such byte among this thread's share?  (Hardly ever.)  Only then a second pass rewrites.
+      // 0x7F / 0xFF (+-240 in e4m3-fnuz) are NaN to the tensor core: one code down (+-224), and the entry goes on
+      // the stage's list so that the softmax warps add what is missing.  First pass: is any such byte among this
+      // thread's share?  (Hardly ever.)  Only then a second pass rewrites and records.
       uint32_t any = 0;
 #pragma unroll 10
       for (int i = 0; i < kPerThread; ++i) {
@@ -248,12 +256,28 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
                ((v.z & 0x7F7F7F7Fu) + 0x01010101u) | ((v.w & 0x7F7F7F7Fu) + 0x01010101u);
       }
       if (any & 0x80808080u) {
+        int* sat_cnt = reinterpret_cast<int*>(smem + C::kOffSatCnt) + st;
+        uint32_t* sat = reinterpret_cast<uint32_t*>(smem + C::kOffSat) + st * kSatCap;
         for (int i = 0; i < kPerThread; ++i) {
-          uint4 v = tile[i * kCheckThreads + lt];
+          const uint32_t piece = i * kCheckThreads + lt;
+          uint4 v = tile[piece];
           uint32_t* x = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) x[k] -= (((x[k] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u) >> 7;
-          tile[i * kCheckThreads + lt] = v;
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t hit = ((x[k] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u;
+            if (hit == 0u) continue;
+            for (int b = 0; b < 4; ++b) {
+              if (((hit >> (8 * b)) & 0x80u) == 0u) continue;
+              // where this byte sits in the tile: chunk, token row, logical column (the swizzle undone)
+              const uint32_t off = piece * 16u + k * 4u + b;
+              const uint32_t chunk = off / kChunkBytes, row = (off % kChunkBytes) >> 7;
+              const uint32_t col = chunk * 128u + (((((off >> 4) & 7u) ^ (row & 7u)) << 4) | (off & 15u));
+              if (col >= static_cast<uint32_t>(kRowBytes)) continue;  // unused half of the rope chunk
+              const int slot = atomicAdd(sat_cnt, 1);
+              if (slot < kSatCap) sat[slot] = row | (col << 7) | (((x[k] >> (8 * b + 7)) & 1u) << 17);
+            }
+            x[k] -= hit >> 7;
+          }
+          tile[piece] = v;
         }
       }
     } else if (p.use_tma) {
@@ -277,7 +301,7 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
 // MMA issuer (one thread)
 // ---------------------------------------------------------------------------
 template <int kPos>
-__device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
+__device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
   constexpr uint32_t kFmtE4M3 = 0;
   constexpr uint32_t idesc_qk = umma_idesc(kFmtE4M3, kFmtE4M3, 0, 0, kMmaM, C::kN);
@@ -306,6 +330,8 @@ __device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t 
     umma_commit(bars + 8 * (kMSFull + (j & 1)));
   };
   auto issue_pv = [&](int j) {
+    // a saturation correction may have put something into O^T before the first P V (role_softmax)
+    const bool keep = j > 0 || *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kStagesMla) != 0;
     const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
     const uint32_t pt_lo = desc_lo_kmajor(base + C::kOffPT + (j & 1) * C::kN * 128);
 #pragma unroll
@@ -315,7 +341,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint32_t base, uint32_t 
 #pragma unroll
       for (int ks = 0; ks < kTok / 32; ++ks) {
         umma_ss_f8(tmem + (2 + mt) * C::kN, make_desc(a_lo + ((ks * 32 * 128) >> 4)), make_desc(pt_lo + ((ks * 32) >> 4)),
-                   idesc_pv, (j > 0 || ks > 0) ? 1u : 0u);
+                   idesc_pv, (keep || ks > 0) ? 1u : 0u);
       }
     }
     umma_commit(bars + 8 * (kMTileEmpty + (j % kStagesMla)));
@@ -408,7 +434,8 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   float m_ref[R], l_sum[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) m_ref[r] = 0.f, l_sum[r] = 0.f;
-  uint32_t slow = 0;  // exact-maximum rounds so far (phase of their barrier)
+  uint32_t slow = 0;          // exact-maximum rounds so far (phase of their barrier)
+  uint32_t n_sat_rounds = 0;  // tiles with saturated entries so far (phase of their barrier)
 
   for (int j = 0; j < n; ++j) {
     const int buf = j & 1, par = (j >> 1) & 1;
@@ -420,6 +447,32 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     uint32_t d[N];
     tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
     const int tok_abs = (w.tile0 + j) * kTok + tl;
+    // Saturated e4m3-fnuz entries of this tile (the check warps listed them): the tensor core saw +-448 where
+    // the cache says +-480 (in e4m3 units); add the rest of this thread's token by hand, into the first term.
+    const int st = j % kStagesMla;
+#ifdef MLA_NO_SAT
+    const int n_sat = 0;
+#else
+    MA_WAIT_WARP(bars + 8 * (kMTileFull + st), (j / kStagesMla) & 1, 0x79);  // long complete; orders the list reads
+    const int n_sat = min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
+#endif
+    const uint32_t* sat = reinterpret_cast<const uint32_t*>(smem + C::kOffSat) + st * kSatCap;
+    if (n_sat > 0) {
+      for (int e = 0; e < n_sat; ++e) {
+        const uint32_t ent = sat[e];
+        if (static_cast<int>(ent & 127u) != tl) continue;
+        const uint32_t col = (ent >> 7) & 1023u;
+        const float rest = (ent >> 17) ? -kSatResidual : kSatResidual;
+        const uint8_t* qt = smem + C::kOffQT + (col >> 7) * (N * 128);
+#pragma unroll
+        for (int r = 0; r < R; r += 2) {  // the two terms of rows r and r + 1 at this column
+          const float2 a = from_e4m3x2(qt[swz128(r, col & 127u)] | (qt[swz128(r + 1, col & 127u)] << 8));
+          const float2 b = from_e4m3x2(qt[swz128(R + r, col & 127u)] | (qt[swz128(R + r + 1, col & 127u)] << 8));
+          d[r] = __float_as_uint(__uint_as_float(d[r]) + rest * (a.x + b.x));
+          d[r + 1] = __float_as_uint(__uint_as_float(d[r + 1]) + rest * (a.y + b.y));
+        }
+      }
+    }
     float s[R];
     float over = -INFINITY;
 #pragma unroll
@@ -511,21 +564,90 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       pt[swz128(R + r + 1, tl)] = static_cast<uint8_t>(t2[r / 2] >> 8);
     }
     }
+    if (n_sat > 0) {  // uniform over the CTA
+      // O^T misses p * (+-32) for every listed entry with a latent column.  The entry's output dimension is a
+      // lane of tensor memory: the warp that owns the lane patches it, with p read back from P^T (both terms
+      // keep their own accumulator column).  P^T must be complete, and no P V may be in flight on O^T.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * (kMSat + (n_sat_rounds & 1)));
+      MA_WAIT_WARP(bars + 8 * (kMSat + (n_sat_rounds & 1)), (n_sat_rounds >> 1) & 1, 0x77);
+      ++n_sat_rounds;
+      if (j > 0) {
+        MA_WAIT_WARP(bars + 8 * (kMPvDone + ((j - 1) & 1)), ((j - 1) >> 1) & 1, 0x78);
+        tc_fence_after_sync();
+      } else {
+        // The first P V of a part normally overwrites O^T.  Start it from zero here and tell the MMA thread to
+        // accumulate instead, so that the patches below survive.
+        uint32_t zero[N];
+#pragma unroll
+        for (int n = 0; n < N; ++n) zero[n] = 0u;
+#pragma unroll 1
+        for (int mt = 0; mt < 4; ++mt) {
+          if constexpr (N == 32) {
+            tmem_st32(tmem + (2 + mt) * N + lane_sel, zero);
+          } else {
+            tmem_st32_at<0>(tmem + (2 + mt) * N + lane_sel, zero);
+            tmem_st32_at<32>(tmem + (2 + mt) * N + lane_sel + 32, zero);
+          }
+        }
+        tmem_st_wait();
+        if (tl == 0) *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kStagesMla) = 1;
+      }
+      for (int e = 0; e < n_sat; ++e) {
+        const uint32_t ent = sat[e];
+        const uint32_t tok = ent & 127u, col = (ent >> 7) & 1023u;
+        if (col >= static_cast<uint32_t>(kLat) || ((col >> 5) & 3u) != static_cast<uint32_t>(warp)) continue;  // warp-uniform
+        const float rest = (ent >> 17) ? -kSatResidual : kSatResidual;
+        const uint32_t taddr = tmem + (2 + (col >> 7)) * N + lane_sel;
+        uint32_t o[N];
+        tmem_load_cols<N>(taddr, o);
+        if (static_cast<uint32_t>(lane) == (col & 31u)) {
+#pragma unroll
+          for (int n = 0; n < N; n += 2) {
+            const float2 pq = from_e4m3x2(pt[swz128(n, tok)] | (pt[swz128(n + 1, tok)] << 8));
+            o[n] = __float_as_uint(__uint_as_float(o[n]) + rest * pq.x);
+            o[n + 1] = __float_as_uint(__uint_as_float(o[n + 1]) + rest * pq.y);
+          }
+        }
+        if constexpr (N == 32) {
+          tmem_st32(taddr, o);
+        } else {
+          tmem_st32_at<0>(taddr, o);
+          tmem_st32_at<32>(taddr + 32, o);
+        }
+        tmem_st_wait();
+      }
+      tc_fence_before_sync();
+      if (tl == 0) *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st) = 0;  // the stage's next tile starts empty
+    }
     fence_proxy_async_smem();
     tc_fence_before_sync();
     mbar_arrive(bars + 8 * (kMPFull + buf));
     MLA_TRACE_AT(j * 8 + 6, tr);
   }
 
-  // epilogue: un-normalised fp32 partial outputs, reference maximum and denominator of every row
+  // epilogue.  With one KV part the CTA finishes its rows itself (normalise, scale back, round to bf16); with
+  // several it leaves un-normalised fp32 outputs, reference maxima and denominators for mla_merge_kernel.
   const size_t slot = blockIdx.x;
   float* part_o = p.part_o + slot * (static_cast<size_t>(R) * kLat);
   float2* part_ml = reinterpret_cast<float2*>(p.part_ml) + slot * R;
-  if (n == 0) {
-    if (tl < R) part_ml[tl] = make_float2(-INFINITY, 0.f);
+  const bool direct = p.parts == 1;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat);
+  auto out_row = [&](int r) {  // row r of this CTA: position pos0 + r / 16, head r % 16
+    return ((static_cast<size_t>(w.brow) * w.q_len + w.pos0 + r / kHeadsMax) * w.heads + (r % kHeadsMax)) * kLat;
+  };
+  auto row_live = [&](int r) { return (r % kHeadsMax) < w.heads && w.pos0 + r / kHeadsMax < w.q_len; };
+  if (n == 0) {  // no token in range (an empty part, or a request without tokens)
+    if (direct) {
+      for (int r = 0; r < R; ++r)
+        if (row_live(r))
+          for (int mt = 0; mt < 4; ++mt) out[out_row(r) + mt * 128 + tl] = __float2bfloat16_rn(0.f);
+    } else if (tl < R) {
+      part_ml[tl] = make_float2(-INFINITY, 0.f);
+    }
     return;
   }
-  // denominators: sum over the 128 tokens-of-a-tile threads
+  // denominators: sum over the 128 tokens-of-a-tile threads, then across the four warps through shared memory
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     float v = l_sum[r];
@@ -533,21 +655,29 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     if (lane == (r & 31)) l_part[warp * R + r] = v;
   }
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bars + 8 * kMEpi);
+  MA_WAIT_WARP(bars + 8 * kMEpi, 0, 0x76);
   MA_WAIT_WARP(bars + 8 * (kMPvDone + ((n - 1) & 1)), ((n - 1) >> 1) & 1, 0x74);
   tc_fence_after_sync();
+  const float fmt = p.kv_format == 0 ? 2.f : 1.f;
 #pragma unroll 1
   for (int mt = 0; mt < 4; ++mt) {
     uint32_t o[N];
     tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
 #pragma unroll
-    for (int r = 0; r < R; ++r)
-      part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
+    for (int r = 0; r < R; ++r) {
+      const float v = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
+      if (direct) {
+        const float l = (l_part[r] + l_part[R + r]) + (l_part[2 * R + r] + l_part[3 * R + r]);
+        const float inv = (l > 0.f || l != l) ? p.kv_scale / (fmt * l) : 0.f;
+        if (row_live(r)) out[out_row(r) + mt * 128 + tl] = __float2bfloat16_rn(v * inv);
+      } else {
+        part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = v;
+      }
+    }
   }
-  // the four warps' denominators meet through shared memory; the flag barrier of the unused parity orders them
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bars + 8 * kMEpi);
-  MA_WAIT_WARP(bars + 8 * kMEpi, 0, 0x76);
-  if (tl < R) {
+  if (!direct && tl < R) {
     const float l = (l_part[tl] + l_part[R + tl]) + (l_part[2 * R + tl] + l_part[3 * R + tl]);
     float m = 0.f;
 #pragma unroll
@@ -578,27 +708,38 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
       if (i >= kMTileFull && i < kMTileFull + kStagesMla) count = kCheckThreads;
       if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = p.use_tma ? 1u : static_cast<uint32_t>(kCopyThreads);
       if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
-      if (i >= kMMx && i <= kMEpi) count = 4;
+      if (i >= kMMx && i < kMNumBars) count = 4;
       mbar_init(bars + 8 * i, count);
     }
     abort_flag_s = 0;
+    for (int i = 0; i < 4; ++i) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
     mbar_fence_init();
   }
   if (warp == 4) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
     tmem_relinquish();
   }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_slot;
+  constexpr int kFirstCopyWarp = 5, kFirstCheckWarp = 5 + kCopyThreads / 32;
 
-  // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a row
-  // is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
-  // q * f = q1 + q2 exact for every element within 2^-7 of the largest (8 significant bits = 4 + 4).
-  {
+  // The copy warps start fetching at once; the other nine warps first turn the query rows into Q^T.
+  if (warp >= kFirstCopyWarp && warp < kFirstCheckWarp) {
+    role_copy<kPos>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
+  } else {
+    // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a
+    // row is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
+    // q * f = q1 + q2 exact for every element within 2^-7 of the largest (8 significant bits = 4 + 4).
     const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
     const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
     float* row_scale = reinterpret_cast<float*>(smem + C::kOffRowScale);
     uint8_t* qt = smem + C::kOffQT;
     const float fmt = p.kv_format == 0 ? 2.f : 1.f;  // e4m3-fnuz bytes read as e4m3 are twice their value
-    for (int r = warp; r < R; r += kThreadsMla / 32) {
+    constexpr int kPrepWarps = kThreadsMla / 32 - kCopyThreads / 32;  // 9
+    const int prep_warp = warp < kFirstCopyWarp ? warp : warp - kCopyThreads / 32;
+    for (int r = prep_warp; r < R; r += kPrepWarps) {
       const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
       const bool live = h < w.heads && pos < w.q_len;
       const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
@@ -634,23 +775,17 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
         }
       }
     }
+    fence_proxy_async_smem();
+    // every one of these nine warps gets here unconditionally: a plain named barrier is safe
+    asm volatile("bar.sync 1, %0;" ::"n"(kPrepWarps * 32) : "memory");
+    if (warp < 4) {
+      role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
+    } else if (warp == 4) {
+      if (lane == 0) role_mma<kPos>(w, smem, base, tmem, ctx);
+    } else {
+      role_check<kPos>(p, w, base, smem, tid - kFirstCheckWarp * 32, ctx);
+    }
   }
-  fence_proxy_async_smem();
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_slot;
-
-  if (warp < 4) {
-    role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
-  } else if (warp == 4) {
-    if (lane == 0) role_mma<kPos>(w, base, tmem, ctx);
-  } else if (warp < 5 + kCopyThreads / 32) {
-    role_copy<kPos>(p, w, base, tid - (kSoftmaxThreads + 32), ctx);
-  } else {
-    role_check<kPos>(p, w, base, smem, tid - (kSoftmaxThreads + 32 + kCopyThreads), ctx);
-  }
-
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem, C::kTmemCols);
@@ -699,7 +834,7 @@ cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
   if (e != cudaSuccess) return e;
   mla_decode_kernel<kPos><<<p.batch * p.groups * p.parts, kThreadsMla, smem_bytes, stream>>>(p);
   e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess || p.parts == 1) return e;  // a single part writes the final output itself
   mla_merge_kernel<<<p.batch * p.q_len * p.heads, 128, 0, stream>>>(p, kPos);
   return cudaGetLastError();
 }

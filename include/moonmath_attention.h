@@ -199,8 +199,9 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
  *                 (no host read, fixed grid: the call can be captured in a CUDA graph with `parts` fixed).
  *   rows: optional int32[batch], batch row of q_lat / o_lat that request b uses (null: b).
  *   kv_format: 0 = e4m3-fnuz, the reference's cache format; 1 = e4m3 (OCP).  The tensor core reads e4m3: fnuz
- *     bytes are reinterpreted (every finite value is exactly half), except 0x7F / 0xFF (+-240) which are
- *     rewritten to +-224, and 0x80 (NaN) which reads as zero.
+ *     bytes are reinterpreted (every finite value is exactly half).  0x7F / 0xFF (+-240), which are NaN in e4m3,
+ *     are fed as +-224 and corrected by hand: exact for up to 640 such entries per 96 consecutive tokens of a
+ *     request, +-224 for the surplus.  0x80 (NaN in fnuz) reads as zero.
  *   parts: KV split per request, 1..MA_MLA_MAX_PARTS (ma_mla_plan_parts); workspace: ma_mla_workspace_bytes.
  */
 #define MA_MLA_MAX_PARTS 64

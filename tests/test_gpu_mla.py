@@ -189,29 +189,32 @@ def test_e4m3_cache_is_read_unchanged(ma, cuda_device):
     _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B, "fn"), "e4m3fn cache")
 
 
-def test_saturated_fnuz_codes_do_not_turn_into_nan(ma, cuda_device):
-    """0x7F / 0xFF are +-240 in e4m3-fnuz and NaN in the format the tensor core reads; the kernel rewrites them
-    to +-224.  With one entry in a hundred saturated the result stays finite and close to the exact one."""
-    B, S, H = 1, 1024, 16
+@pytest.mark.parametrize("paged", [False, True])
+@pytest.mark.parametrize("density,exact", [(0.0005, True), (0.005, True), (0.05, False)])
+def test_saturated_fnuz_codes_are_corrected(ma, cuda_device, paged, density, exact):
+    """0x7F / 0xFF are +-240 in e4m3-fnuz and NaN in the format the tensor core reads.  The kernel feeds +-224 and
+    adds the rest by hand for up to 640 entries per 96-token tile: exact below that, finite and close above."""
+    B, S, H = 2, 1000, 16
     kv = _rand_kv(B, S, cuda_device, 37)
     raw = kv.view(torch.uint8)
     g = torch.Generator().manual_seed(3)
-    hit = (torch.rand(raw.shape, generator=g) < 0.01).to(cuda_device)
+    hit = (torch.rand(raw.shape, generator=g) < density).to(cuda_device)
     sign = (torch.rand(raw.shape, generator=g) < 0.5).to(cuda_device)
     raw[hit & sign] = 0x7F
     raw[hit & ~sign] = 0xFF
+    kv_scale = 1.0 / 512.0  # keeps the softmax spread out although some keys are huge
     q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 37)
-    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, 1.0 / 512.0)  # a scale that keeps the softmax spread out
-    out = o_lat.float().cpu().numpy()
+    if paged:
+        pool, kv_indices, kv_indptr = _paged_pool(kv, [S] * B, cuda_device, 37)
+        lens = torch.tensor([S] * B, dtype=torch.int32, device=cuda_device)
+        ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, 2, SCALE, kv_scale)
+    else:
+        ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, kv_scale)
+    out = o_lat.float().cpu().numpy().reshape(B, 1, H, LAT)
     assert ma.last_status()[0] == 0 and np.isfinite(out).all()
     qa, qb = q_lat.unsqueeze(1).float().cpu().numpy(), q_pe.unsqueeze(1).float().cpu().numpy()
-    # the documented behaviour, exactly: the same cache with the two codes moved one down
-    moved = raw.cpu().numpy().copy()
-    moved[moved == 0x7F] = 0x7E
-    moved[moved == 0xFF] = 0xFE
-    assert mo.rel_l2(out.reshape(1, 1, H, LAT), mo.mla_decode(qa, qb, moved, [S], SCALE, 1.0 / 512.0)) < REL_L2
-    # ... and how far that is from the true values when one entry in a hundred is saturated (240 -> 224 is 6.7 %)
-    assert mo.rel_l2(out.reshape(1, 1, H, LAT), mo.mla_decode(qa, qb, raw.cpu().numpy(), [S], SCALE, 1.0 / 512.0)) < 0.1
+    err = mo.rel_l2(out, mo.mla_decode(qa, qb, raw.cpu().numpy(), [S] * B, SCALE, kv_scale))
+    assert err < (REL_L2 if exact else 0.1), err
 
 
 def test_contiguous_argument_errors(ma, cuda_device):
