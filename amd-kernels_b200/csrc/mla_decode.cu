@@ -24,7 +24,7 @@
 // e4m3 caches (kv_format 1) are read unchanged.
 //
 // One CTA per (request, group of draft positions, KV part); parts are merged by mla_merge_kernel.
-//   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12  copy    warps 13-16  check
+//   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12 (or 5)  copy    then four check warps
 // All waits are bounded mbarrier waits.
 #include <cuda_fp8.h>
 
@@ -44,8 +44,11 @@ constexpr int kChunkBytes = kTok * 128;          // 12 KiB
 constexpr int kTileBytesMla = kChunks * kChunkBytes;
 constexpr int kStagesMla = 3;                    // a tile spends about as long being loaded and checked as being used
 constexpr int kHeadsMax = 16;
-constexpr int kSoftmaxThreads = 128, kCopyThreads = 256, kCheckThreads = 128;
-constexpr int kThreadsMla = kSoftmaxThreads + 32 + kCopyThreads + kCheckThreads;  // 544
+constexpr int kSoftmaxThreads = 128, kCheckThreads = 128;
+// Copy warps: eight for the 16-byte copies of a paged pool, one (one thread of it) for box loads; the block is
+// launched with as many threads as its roles need, so the box-load variant has twice the registers per thread.
+constexpr int copy_threads(bool tma) { return tma ? 32 : 256; }
+constexpr int block_threads(bool tma) { return kSoftmaxThreads + 32 + copy_threads(tma) + kCheckThreads; }  // 320 / 544
 constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
 constexpr int kSatCap = 640;                     // saturated e4m3-fnuz entries of one tile that are corrected exactly
 constexpr float kSatResidual = 32.f;             // +-240 fnuz = +-480 as e4m3; the tensor core gets +-448; the rest by hand
@@ -172,11 +175,12 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-template <int kPos>
+template <int kPos, bool kTma>
 __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uint32_t base, int lt, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
+  constexpr int kCopyThreads = copy_threads(kTma);
   const uint32_t bars = base + C::kOffBars;
-  if (p.use_tma) {
+  if constexpr (kTma) {
     // Contiguous slab: five box loads per tile (one per 128-byte column chunk, 96 rows each), issued by one
     // thread.  Rows past the slab and the columns past byte 576 of the rope chunk arrive as zeros.
     if (lt != 0) return;
@@ -192,7 +196,7 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
       MLA_TRACE_AT(4000 + j * 4 + 1, j < 60);
     }
     return;
-  }
+  } else {
   // Paged pool (or a slab sent this way): a warp copies 12 whole token rows of the tile, 36 pieces of 16 bytes
   // each.  Lane k < 12 holds the pool slot of the warp's k-th row, fetched one tile ahead, so that no copy
   // waits for an index load of its own.
@@ -230,9 +234,10 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     cp_async_arrive(bars + 8 * (kMTileRaw + st));
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
   }
+  }
 }
 
-template <int kPos>
+template <int kPos, bool kTma>
 __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, uint32_t base, uint8_t* smem, int lt,
                                            const WaitCtx& ctx) {
   using C = Cfg<kPos>;
@@ -280,7 +285,7 @@ __device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, ui
           tile[piece] = v;
         }
       }
-    } else if (p.use_tma) {
+    } else if (kTma) {
       // An e4m3 cache keeps its NaN codes.  Box loads bring whole rows, also those between the end of the
       // request and the end of the slab, which nobody wrote for this request: zero them (P = 0 meets them).
       const int live_rows = w.end_max - (w.tile0 + j) * kTok;
@@ -450,12 +455,9 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     // Saturated e4m3-fnuz entries of this tile (the check warps listed them): the tensor core saw +-448 where
     // the cache says +-480 (in e4m3 units); add the rest of this thread's token by hand, into the first term.
     const int st = j % kStagesMla;
-#ifdef MLA_NO_SAT
-    const int n_sat = 0;
-#else
-    MA_WAIT_WARP(bars + 8 * (kMTileFull + st), (j / kStagesMla) & 1, 0x79);  // long complete; orders the list reads
-    const int n_sat = min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
-#endif
+    // The count was written before the check warps passed the tile on; the MMA thread waited for that before
+    // it issued the Q K^T whose completion this thread has just waited for.  e4m3 caches have no such entries.
+    const int n_sat = p.kv_format != 0 ? 0 : min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
     const uint32_t* sat = reinterpret_cast<const uint32_t*>(smem + C::kOffSat) + st * kSatCap;
     if (n_sat > 0) {
       for (int e = 0; e < n_sat; ++e) {
@@ -475,11 +477,17 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     }
     float s[R];
     float over = -INFINITY;
+    float scale_r[R];  // four 16-byte loads instead of sixteen scalar ones: shared-memory instructions are what this loop waits for
+#pragma unroll
+    for (int r = 0; r < R; r += 4) {
+      const float4 q4 = *reinterpret_cast<const float4*>(row_scale + r);
+      scale_r[r] = q4.x, scale_r[r + 1] = q4.y, scale_r[r + 2] = q4.z, scale_r[r + 3] = q4.w;
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       // position (r / 16) of the group sees tokens [0, len - q_len + pos + 1)
       const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
-      const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * row_scale[r];
+      const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * scale_r[r];
       s[r] = (tl < kTok && tok_abs < limit) ? v : -INFINITY;
       over = fmaxf(over, s[r] - m_ref[r]);
     }
@@ -687,9 +695,10 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   }
 }
 
-template <int kPos>
-__global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
+template <int kPos, bool kTma>
+__global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
   using C = Cfg<kPos>;
+  constexpr int kCopyThreads = copy_threads(kTma), kThreadsMla = block_threads(kTma);
   constexpr int R = C::kRows, N = C::kN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -706,7 +715,7 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
     for (uint32_t i = 0; i < kMNumBars; ++i) {
       uint32_t count = 1;
       if (i >= kMTileFull && i < kMTileFull + kStagesMla) count = kCheckThreads;
-      if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = p.use_tma ? 1u : static_cast<uint32_t>(kCopyThreads);
+      if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
       if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
       if (i >= kMMx && i < kMNumBars) count = 4;
       mbar_init(bars + 8 * i, count);
@@ -727,7 +736,7 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
 
   // The copy warps start fetching at once; the other nine warps first turn the query rows into Q^T.
   if (warp >= kFirstCopyWarp && warp < kFirstCheckWarp) {
-    role_copy<kPos>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
+    role_copy<kPos, kTma>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
   } else {
     // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a
     // row is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
@@ -783,7 +792,7 @@ __global__ void __launch_bounds__(kThreadsMla, 1) mla_decode_kernel(const __grid
     } else if (warp == 4) {
       if (lane == 0) role_mma<kPos>(w, smem, base, tmem, ctx);
     } else {
-      role_check<kPos>(p, w, base, smem, tid - kFirstCheckWarp * 32, ctx);
+      role_check<kPos, kTma>(p, w, base, smem, tid - kFirstCheckWarp * 32, ctx);
     }
   }
   tc_fence_before_sync();
@@ -824,15 +833,15 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int k
   for (int k = 0; k < 4; ++k) out[k * 128 + threadIdx.x] = __float2bfloat16_rn(acc[k] * inv);
 }
 
-template <int kPos>
+template <int kPos, bool kTma>
 cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
   using C = Cfg<kPos>;
   constexpr size_t smem_bytes = C::kOffBars + kMNumBars * 8 + 1024;
   static_assert(smem_bytes <= 232448, "shared memory budget of one CTA on sm_100");
-  cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel<kPos>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel<kPos, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_bytes));
   if (e != cudaSuccess) return e;
-  mla_decode_kernel<kPos><<<p.batch * p.groups * p.parts, kThreadsMla, smem_bytes, stream>>>(p);
+  mla_decode_kernel<kPos, kTma><<<p.batch * p.groups * p.parts, block_threads(kTma), smem_bytes, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.parts == 1) return e;  // a single part writes the final output itself
   mla_merge_kernel<<<p.batch * p.q_len * p.heads, 128, 0, stream>>>(p, kPos);
@@ -849,7 +858,7 @@ extern "C" int ma_trace_read_mla(unsigned long long* host, int n) {
 
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
   if (p.pos_per_cta != 1) return cudaErrorInvalidValue;  // only the one-position instance is built
-  return launch_one<1>(p, stream);
+  return p.use_tma ? launch_one<1, true>(p, stream) : launch_one<1, false>(p, stream);
 }
 
 }  // namespace ma
