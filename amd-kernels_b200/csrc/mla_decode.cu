@@ -634,6 +634,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     MLA_TRACE_AT(j * 8 + 6, tr);
   }
 
+  MLA_TRACE_AT(5003, tl == 0);
   // epilogue.  With one KV part the CTA finishes its rows itself (normalise, scale back, round to bf16); with
   // several it leaves un-normalised fp32 outputs, reference maxima and denominators for mla_merge_kernel.
   const size_t slot = blockIdx.x;
@@ -669,22 +670,41 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   MA_WAIT_WARP(bars + 8 * (kMPvDone + ((n - 1) & 1)), ((n - 1) >> 1) & 1, 0x74);
   tc_fence_after_sync();
   const float fmt = p.kv_format == 0 ? 2.f : 1.f;
+  float inv[R];  // per row: kv_scale / (format factor x denominator); 0 for a row without tokens
+  bool live[R];
+#pragma unroll
+  for (int r = 0; r < R; r += 4) {
+    float4 l4 = *reinterpret_cast<const float4*>(l_part + r);
+#pragma unroll
+    for (int q = 1; q < 4; ++q) {
+      const float4 x = *reinterpret_cast<const float4*>(l_part + q * R + r);
+      l4.x += x.x, l4.y += x.y, l4.z += x.z, l4.w += x.w;
+    }
+    const float l[4] = {l4.x, l4.y, l4.z, l4.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      inv[r + q] = (l[q] > 0.f || l[q] != l[q]) ? p.kv_scale / (fmt * l[q]) : 0.f;
+      live[r + q] = row_live(r + q);
+    }
+  }
 #pragma unroll 1
   for (int mt = 0; mt < 4; ++mt) {
     uint32_t o[N];
     tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
+    if (direct) {
+      __nv_bfloat16* dst = out + out_row(0) + mt * 128 + tl;  // rows of one position are consecutive heads
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const float v = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
-      if (direct) {
-        const float l = (l_part[r] + l_part[R + r]) + (l_part[2 * R + r] + l_part[3 * R + r]);
-        const float inv = (l > 0.f || l != l) ? p.kv_scale / (fmt * l) : 0.f;
-        if (row_live(r)) out[out_row(r) + mt * 128 + tl] = __float2bfloat16_rn(v * inv);
-      } else {
-        part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = v;
+      for (int r = 0; r < R; ++r) {
+        const float v = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
+        if (live[r]) dst[(static_cast<size_t>(r / kHeadsMax) * w.heads + (r % kHeadsMax)) * kLat] = __float2bfloat16_rn(v * inv[r]);
       }
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
     }
   }
+  MLA_TRACE_AT(5004, tl == 0);
   if (!direct && tl < R) {
     const float l = (l_part[tl] + l_part[R + tl]) + (l_part[2 * R + tl] + l_part[3 * R + tl]);
     float m = 0.f;
@@ -709,6 +729,7 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const WaitCtx ctx{p.status, abort_flag};
   const Work w = decode_work(p, kPos);
+  MLA_TRACE_AT(5000, tid == 0);
 
   if (tid == 0) {
     const uint32_t bars = base + C::kOffBars;
@@ -732,6 +753,7 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
+  MLA_TRACE_AT(5001, tid == 0);
   constexpr int kFirstCopyWarp = 5, kFirstCheckWarp = 5 + kCopyThreads / 32;
 
   // The copy warps start fetching at once; the other nine warps first turn the query rows into Q^T.
@@ -748,18 +770,33 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
     const float fmt = p.kv_format == 0 ? 2.f : 1.f;  // e4m3-fnuz bytes read as e4m3 are twice their value
     constexpr int kPrepWarps = kThreadsMla / 32 - kCopyThreads / 32;  // 9
     const int prep_warp = warp < kFirstCopyWarp ? warp : warp - kCopyThreads / 32;
-    for (int r = prep_warp; r < R; r += kPrepWarps) {
+    constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 2: a warp takes rows prep_warp and prep_warp + 9
+    float2 vin[kRounds][9];  // 576 / 64: lane holds columns 64 i + 2 lane, + 1; all loads are issued before any is used
+#pragma unroll
+    for (int k = 0; k < kRounds; ++k) {
+      const int r = prep_warp + k * kPrepWarps;
       const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
-      const bool live = h < w.heads && pos < w.q_len;
+      const bool live = r < R && h < w.heads && pos < w.q_len;
       const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
-      float v[18];  // 576 / 32
+#pragma unroll
+      for (int i = 0; i < 9; ++i) {
+        const int x = i * 64 + lane * 2;
+        vin[k][i] = make_float2(0.f, 0.f);
+        if (live) {
+          const __nv_bfloat162 two = x < kLat ? *reinterpret_cast<const __nv_bfloat162*>(q_lat + qrow * kLat + x)
+                                              : *reinterpret_cast<const __nv_bfloat162*>(q_pe + qrow * 64 + (x - kLat));
+          vin[k][i] = __bfloat1622float2(two);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kRounds; ++k) {
+      const int r = prep_warp + k * kPrepWarps;
+      if (r >= R) break;
+      const float2* v = vin[k];
       float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 18; ++i) {
-        const int x = i * 32 + lane;
-        v[i] = !live ? 0.f : (x < kLat ? __bfloat162float(q_lat[qrow * kLat + x]) : __bfloat162float(q_pe[qrow * 64 + (x - kLat)]));
-        amax = fmaxf(amax, fabsf(v[i]));
-      }
+      for (int i = 0; i < 9; ++i) amax = fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       // f = 2^(7 - exponent(amax)); NaN / inf / zero rows keep f = 1
@@ -770,23 +807,21 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
       }
       if (lane == 0) row_scale[r] = p.scale * 1.4426950408889634f * p.kv_scale / (fmt * f);
 #pragma unroll
-      for (int i = 0; i < 18; i += 2) {
-        const float a = v[i] * f, b = v[i + 1] * f;
+      for (int i = 0; i < 9; ++i) {
+        const float a = v[i].x * f, b = v[i].y * f;
         const uint32_t t1 = to_e4m3x2(a, b);
         const float2 back = from_e4m3x2(t1);
         const uint32_t t2 = to_e4m3x2(a - back.x, b - back.y);
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t x = (i + k) * 32 + lane;
-          const uint32_t chunk = x >> 7, col = x & 127u;
-          qt[chunk * (N * 128) + swz128(r, col)] = static_cast<uint8_t>((t1 >> (8 * k)) & 0xFF);
-          qt[chunk * (N * 128) + swz128(R + r, col)] = static_cast<uint8_t>((t2 >> (8 * k)) & 0xFF);
-        }
+        const uint32_t x = i * 64 + lane * 2;
+        const uint32_t chunk = x >> 7, col = x & 127u;  // two adjacent bytes of one 16-byte piece
+        *reinterpret_cast<uint16_t*>(qt + chunk * (N * 128) + swz128(r, col)) = static_cast<uint16_t>(t1);
+        *reinterpret_cast<uint16_t*>(qt + chunk * (N * 128) + swz128(R + r, col)) = static_cast<uint16_t>(t2);
       }
     }
     fence_proxy_async_smem();
     // every one of these nine warps gets here unconditionally: a plain named barrier is safe
     asm volatile("bar.sync 1, %0;" ::"n"(kPrepWarps * 32) : "memory");
+    MLA_TRACE_AT(5002, tid == 0);
     if (warp < 4) {
       role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
     } else if (warp == 4) {
