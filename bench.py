@@ -2,7 +2,7 @@
 """Benchmark of `moonmath_attention.forward` on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c2|c4|c5] [--round-mode rtne|rtna|rtz]
+                    [--workload c2|c4|c5|mla] [--round-mode rtne|rtna|rtz]
 
 A step is one `forward` call over one batch of synthetic input.  The default
 workload is the headline shape (2, 24, 8192, 128) bf16 BSHD, one whole problem
@@ -206,19 +206,149 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+# MLA absorbed decode (a side workload, not the headline): one decode step of 148 requests of 4096 cached tokens,
+# 16 heads, e4m3-fnuz cache as the reference stores it.  HBM-bound: every 576-byte row is read once.
+MLA_SHAPE = {"batch": 148, "seq": 4096, "heads": 16}
+# dram__bytes_read.sum + dram__bytes_write.sum of one mla_decode_kernel launch at that shape (profiles/mla_decode_b200.md)
+MLA_NCU_TRAFFIC_BYTES = 351978752 + 4113664
+
+
+def mla_cpu_oracle_rate(budget_s: float) -> dict:
+    """Times the CPU oracle (numpy, BLAS threads) on whole requests of the MLA workload; GB/s of KV cache."""
+    import numpy as np
+
+    from oracle import mla_oracle as mo
+
+    S, H = MLA_SHAPE["seq"], MLA_SHAPE["heads"]
+    rng = np.random.default_rng(0)
+    kv = rng.integers(0, 256, size=(1, S, 576), dtype=np.uint8)
+    kv[kv == 0x80] = 0
+    q_lat = rng.standard_normal((1, 1, H, 512)).astype(np.float32)
+    q_pe = rng.standard_normal((1, 1, H, 64)).astype(np.float32)
+    mo.mla_decode(q_lat, q_pe, kv, [S], 576 ** -0.5, 1 / 32)
+    n, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < budget_s:
+        mo.mla_decode(q_lat, q_pe, kv, [S], 576 ** -0.5, 1 / 32)
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n * S * 576 / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{n} requests of {S} cached tokens (of the workload's {MLA_SHAPE['batch']}), numpy oracle, {dt:.1f} s"}
+
+
+def run_mla(args) -> None:
+    """`--workload mla`: GB/s of KV cache through mla_decode_a16w8 on every rank's own batch (weak scaling)."""
+    B, S, H = MLA_SHAPE["batch"], MLA_SHAPE["seq"], MLA_SHAPE["heads"]
+    traffic = B * S * 576
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        if rank == 0:
+            base = mla_cpu_oracle_rate(15.0)
+            print(json.dumps({"impl": "reference", "metric": "GB/s of KV cache per mla_decode_a16w8 call", "value": base["value"],
+                              "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8 x bf16 -> f32",
+                              "data": "synthetic", "config": {"workload": f"mla decode, requests of {S} tokens, {H} heads"},
+                              "cpu_baseline": base, "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0,
+                                                            "d2h_bytes_per_step": 0}}), flush=True)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; moonmath_attention has no CPU path")
+    import moonmath_attention as ma
+    from moonmath_attention.shard import max_over_ranks
+
+    rank, world, local = dist_setup(args.gpus)
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    warmup = max(3, args.warmup)
+    g = torch.Generator(device=dev)
+    g.manual_seed(42 * 1000003 + rank)
+    kv = torch.randn(B, S, 576, generator=g, device=dev).to(torch.float8_e4m3fnuz)  # 349 MB: larger than L2
+    q_lat = (torch.randn(B, H, 512, generator=g, device=dev) * 3).bfloat16()
+    q_pe = (torch.randn(B, H, 64, generator=g, device=dev) * 3).bfloat16()
+    o_lat = torch.zeros_like(q_lat)
+    scale, kv_scale = 576 ** -0.5, 1.0 / 32.0
+    step = lambda: ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, scale, kv_scale)
+    sampler = ClockSampler(local)
+    for _ in range(warmup):
+        step()
+    barrier(world)
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        step()
+    b.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    ms_rank = a.elapsed_time(b) / args.steps
+    ms = max_over_ranks(ms_rank, world)
+    status = ma.last_status()
+    # end to end: the cache is state that lives on the device between decode steps; a step brings the queries
+    # from pinned host memory and takes the outputs back
+    hq_lat, hq_pe = q_lat.cpu().pin_memory(), q_pe.cpu().pin_memory()
+    ho = torch.empty_like(hq_lat).pin_memory()
+
+    def e2e_step():
+        q_lat.copy_(hq_lat, non_blocking=True)
+        q_pe.copy_(hq_pe, non_blocking=True)
+        step()
+        ho.copy_(o_lat, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    a.record()
+    for _ in range(args.steps):
+        e2e_step()
+    b.record()
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks(a.elapsed_time(b) / args.steps, world)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]) if os.path.exists(
+            os.path.join(ROOT, "MEASURED_PEAKS.json")) else 6650.0
+        achieved = traffic / ms_rank / 1e6
+        line = {
+            "metric": "GB/s of KV cache per mla_decode_a16w8 call", "value": world * traffic / ms / 1e6, "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp8 (e4m3-fnuz) cache x bf16 queries, f32 accumulation",
+            "data": "synthetic N(0,1) cache quantised to e4m3-fnuz, queries N(0,9), seeded per rank",
+            "config": {"workload": f"mla decode: batch {B} x {S} cached tokens, q_len 1, {H} heads, contiguous slab, per GPU",
+                       "l2": "cache (349 MB) larger than L2 (no flush needed)"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": MLA_NCU_TRAFFIC_BYTES, "bytes_per_launch": traffic,
+                         "peak_source": "measured hbm_gbs" if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else "fallback"},
+            "e2e": {"value": world * traffic / e2e_ms / 1e6, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": hq_lat.numel() * 2 + hq_pe.numel() * 2, "d2h_bytes_per_step": ho.numel() * 2,
+                    "note": "the KV cache is device-resident state; queries in and outputs out cross PCIe every step"},
+            "gpu_launches": args.steps, "device_status": status[:3], "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = mla_cpu_oracle_rate(12.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS) + ["mla"])
     ap.add_argument("--round-mode", default="rtne", choices=["rtne", "rtna", "rtz"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-modes", action="store_true", help="skip the per-rounding-mode timing loops")
     args = ap.parse_args()
 
+    if args.workload == "mla":
+        run_mla(args)
+        return
     if args.impl == "reference":
         rank = int(os.environ.get("RANK", "0"))
         run_reference(args, rank, int(os.environ.get("WORLD_SIZE", "1")))
