@@ -18,13 +18,14 @@
 //
 // e4m3-fnuz (the reference's format) differs from the e4m3 the tensor core reads by a factor of two in
 // every finite value, folded into the scales, and in two codes: 0x7F / 0xFF are +-240 there and NaN here.
-// The check warps rewrite them to 0x7E / 0xFE (+-224) and list them; the softmax warps add the missing
-// +-16 x q to the scores and +-16 x p to the outputs by hand, so the result is exact for up to 640 such
-// entries per tile of 96 tokens (beyond that the rest stay at +-224).  0x80 (NaN there) reads as zero.
-// e4m3 caches (kv_format 1) are read unchanged.
+// Nobody looks for them in advance: a token row that holds one gives NaN scores, and only then does the
+// softmax thread of that token rewrite them to 0x7E / 0xFE (+-224) in shared memory, list them and have the
+// tile's Q K^T run again; the softmax warps add the missing +-16 x q to the scores and +-16 x p to the outputs
+// by hand, so the result is exact for up to 640 such entries per tile of 96 tokens (beyond that the rest stay
+// at +-224).  0x80 (NaN there) reads as zero.  e4m3 caches (kv_format 1) are read unchanged.
 //
 // One CTA per (request, group of draft positions, KV part); parts are merged by mla_merge_kernel.
-//   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12 (or 5)  copy    then four check warps
+//   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12 (or 5)  copy
 // All waits are bounded mbarrier waits.
 #include <cuda_fp8.h>
 
@@ -42,13 +43,13 @@ constexpr int kMmaM = 128;                       // rows of an MMA; S^T rows 96.
 constexpr int kChunks = 5;                       // 128-byte column chunks of a row: 4 latent + rope (64 bytes used)
 constexpr int kChunkBytes = kTok * 128;          // 12 KiB
 constexpr int kTileBytesMla = kChunks * kChunkBytes;
-constexpr int kStagesMla = 3;                    // a tile spends about as long being loaded and checked as being used
+constexpr int kStagesMla = 3;                    // a tile spends about as long being loaded as being used
 constexpr int kHeadsMax = 16;
-constexpr int kSoftmaxThreads = 128, kCheckThreads = 128;
+constexpr int kSoftmaxThreads = 128;
 // Copy warps: eight for the 16-byte copies of a paged pool, one (one thread of it) for box loads; the block is
 // launched with as many threads as its roles need, so the box-load variant has twice the registers per thread.
 constexpr int copy_threads(bool tma) { return tma ? 32 : 256; }
-constexpr int block_threads(bool tma) { return kSoftmaxThreads + 32 + copy_threads(tma) + kCheckThreads; }  // 320 / 544
+constexpr int block_threads(bool tma) { return kSoftmaxThreads + 32 + copy_threads(tma); }  // 192 / 416
 constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
 constexpr int kSatCap = 640;                     // saturated e4m3-fnuz entries of one tile that are corrected exactly
 constexpr float kSatResidual = 32.f;             // +-240 fnuz = +-480 as e4m3; the tensor core gets +-448; the rest by hand
@@ -70,9 +71,8 @@ struct Cfg {
   static constexpr uint32_t kOffBars = kOffSat + kStagesMla * kSatCap * 4;
 };
 enum MlaBar : uint32_t {
-  kMTileFull = 0,   // [3] check warps -> MMA (128 arrivals)
   kMTileEmpty = 3,  // [3] MMA -> copy warps
-  kMTileRaw = 6,    // [3] copy warps -> check warps: the tile has landed (256 copy threads, or 1 + bytes for box loads)
+  kMTileRaw = 6,    // [3] copy warps -> MMA: the tile has landed (256 copy threads, or 1 + bytes for box loads)
   kMSFull = 9,      // [2] MMA -> softmax
   kMPFull = 11,     // [2] softmax -> MMA (128 arrivals)
   kMPvDone = 13,    // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
@@ -80,7 +80,9 @@ enum MlaBar : uint32_t {
   kMFlag = 17,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
   kMEpi = 19,       //     softmax warps among themselves: denominators written (4 arrivals)
   kMSat = 20,       // [2] softmax warps among themselves: P^T written, before a saturation correction (4 arrivals)
-  kMNumBars = 22
+  kMRedoReq = 22,   //     softmax warps -> MMA: rows of the oldest tile were rewritten, run its Q K^T again (4 arrivals)
+  kMRedoDone = 23,  //     MMA -> softmax: that Q K^T has completed
+  kMNumBars = 24
 };
 
 #ifdef MA_TRACE
@@ -163,9 +165,8 @@ __device__ __forceinline__ Work decode_work(const MlaParams& p, int kpos) {
 // ---------------------------------------------------------------------------
 // loaders.  Eight "copy" warps stream a tile of 128 token rows into the swizzled chunks with 16-byte
 // asynchronous copies (no registers in between) and hand completion to an mbarrier, so they never wait for
-// data and the next tile's copies start the moment its stage is free.  Four "check" warps take the landed
-// tile, rewrite the byte codes that need it (e4m3-fnuz only), make the tile visible to the tensor core and
-// pass it on.
+// data and the next tile's copies start the moment its stage is free.  The MMA thread takes the landed tile
+// (after a proxy fence for the 16-byte copies, which are generic-proxy writes; box loads need none).
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
@@ -237,75 +238,10 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
   }
 }
 
-template <int kPos, bool kTma>
-__device__ __forceinline__ void role_check(const MlaParams& p, const Work& w, uint32_t base, uint8_t* smem, int lt,
-                                           const WaitCtx& ctx) {
-  using C = Cfg<kPos>;
-  const uint32_t bars = base + C::kOffBars;
-  const bool fnuz = p.kv_format == 0;
-  constexpr int kPerThread = kTileBytesMla / 16 / kCheckThreads;  // 30 x 16 bytes per tile (the rope chunk's unused half included)
-  for (int j = 0; j < w.tiles; ++j) {
-    const int st = j % kStagesMla;
-    MA_WAIT_SLEEP(32, bars + 8 * (kMTileRaw + st), (j / kStagesMla) & 1, 0x58);
-    MLA_TRACE_AT(4000 + j * 4 + 2, lt == 0 && j < 60);
-    uint4* tile = reinterpret_cast<uint4*>(smem + C::kOffKV + st * kTileBytesMla);
-    if (fnuz) {
-      // 0x7F / 0xFF (+-240 in e4m3-fnuz) are NaN to the tensor core: one code down (+-224), and the entry goes on
-      // the stage's list so that the softmax warps add what is missing.  First pass: is any such byte among this
-      // thread's share?  (Hardly ever.)  Only then a second pass rewrites and records.
-      uint32_t any = 0;
-#pragma unroll 10
-      for (int i = 0; i < kPerThread; ++i) {
-        const uint4 v = tile[i * kCheckThreads + lt];
-        any |= ((v.x & 0x7F7F7F7Fu) + 0x01010101u) | ((v.y & 0x7F7F7F7Fu) + 0x01010101u) |
-               ((v.z & 0x7F7F7F7Fu) + 0x01010101u) | ((v.w & 0x7F7F7F7Fu) + 0x01010101u);
-      }
-      if (any & 0x80808080u) {
-        int* sat_cnt = reinterpret_cast<int*>(smem + C::kOffSatCnt) + st;
-        uint32_t* sat = reinterpret_cast<uint32_t*>(smem + C::kOffSat) + st * kSatCap;
-        for (int i = 0; i < kPerThread; ++i) {
-          const uint32_t piece = i * kCheckThreads + lt;
-          uint4 v = tile[piece];
-          uint32_t* x = reinterpret_cast<uint32_t*>(&v);
-          for (int k = 0; k < 4; ++k) {
-            const uint32_t hit = ((x[k] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u;
-            if (hit == 0u) continue;
-            for (int b = 0; b < 4; ++b) {
-              if (((hit >> (8 * b)) & 0x80u) == 0u) continue;
-              // where this byte sits in the tile: chunk, token row, logical column (the swizzle undone)
-              const uint32_t off = piece * 16u + k * 4u + b;
-              const uint32_t chunk = off / kChunkBytes, row = (off % kChunkBytes) >> 7;
-              const uint32_t col = chunk * 128u + (((((off >> 4) & 7u) ^ (row & 7u)) << 4) | (off & 15u));
-              if (col >= static_cast<uint32_t>(kRowBytes)) continue;  // unused half of the rope chunk
-              const int slot = atomicAdd(sat_cnt, 1);
-              if (slot < kSatCap) sat[slot] = row | (col << 7) | (((x[k] >> (8 * b + 7)) & 1u) << 17);
-            }
-            x[k] -= hit >> 7;
-          }
-          tile[piece] = v;
-        }
-      }
-    } else if (kTma) {
-      // An e4m3 cache keeps its NaN codes.  Box loads bring whole rows, also those between the end of the
-      // request and the end of the slab, which nobody wrote for this request: zero them (P = 0 meets them).
-      const int live_rows = w.end_max - (w.tile0 + j) * kTok;
-      if (live_rows < kTok) {
-        for (int i = lt; i < kTileBytesMla / 16; i += kCheckThreads) {
-          const int row = (i % (kChunkBytes / 16)) / 8;  // 8 pieces of 16 bytes per row and chunk
-          if (row >= live_rows) tile[i] = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-    }
-    fence_proxy_async_smem();
-    mbar_arrive(bars + 8 * (kMTileFull + st));
-    MLA_TRACE_AT(4000 + j * 4 + 3, lt == 0 && j < 60);
-  }
-}
-
 // ---------------------------------------------------------------------------
 // MMA issuer (one thread)
 // ---------------------------------------------------------------------------
-template <int kPos>
+template <int kPos, bool kTma>
 __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t base, uint32_t tmem, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
   constexpr uint32_t kFmtE4M3 = 0;
@@ -317,10 +253,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
   // Q K^T runs with M = 128 over chunks of 96 token rows: rows 96..127 of the A operand are the first 32 rows
   // of whatever follows the chunk in shared memory.  A row of D depends on its own row of A only, so this
   // fills S^T rows 96..127 with numbers nobody reads.  P V has the tokens on K: three steps of 32, exact.
-  // Q K^T runs with M = 128 over chunks of 96 token rows: rows 96..127 of the A operand are the first 32 rows
-  // of whatever follows the chunk in shared memory.  A row of D depends on its own row of A only, so this
-  // fills S^T rows 96..127 with numbers nobody reads.  P V has the tokens on K: three steps of 32, exact.
-  auto issue_qk = [&](int j) {
+  auto issue_qk = [&](int j, uint32_t done_bar) {
     const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
     const uint32_t a_lo = desc_lo_kmajor(tile);
     const uint32_t d = tmem + (j & 1) * C::kN;
@@ -332,7 +265,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
                    make_desc(qt_lo + ((c * C::kN * 128 + ks * 32) >> 4)), idesc_qk, (c | ks) != 0 ? 1u : 0u);
       }
     }
-    umma_commit(bars + 8 * (kMSFull + (j & 1)));
+    umma_commit(done_bar);
   };
   auto issue_pv = [&](int j) {
     // a saturation correction may have put something into O^T before the first P V (role_softmax)
@@ -355,25 +288,40 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
   // Whatever is ready is issued: Q K^T of tile i needs the tile and the S buffer (read out by the softmax of
   // tile i - 2, known from its P arrival, i.e. once P V (i - 2) has been issued); P V of tile j needs P(j).
   int qk_i = 0, pv_i = 0;
+  uint32_t redos = 0;
   uint32_t idle = 0;
   uint64_t t0 = 0;
   while (pv_i < n) {
     bool progressed = false;
     if (qk_i < n && qk_i - pv_i < 2 &&
-        mbar_test_wait(bars + 8 * (kMTileFull + (qk_i % kStagesMla)), (qk_i / kStagesMla) & 1)) {
+        mbar_test_wait(bars + 8 * (kMTileRaw + (qk_i % kStagesMla)), (qk_i / kStagesMla) & 1)) {
+      if constexpr (!kTma) fence_proxy_async_smem();
       tc_fence_after_sync();
       MLA_TRACE_AT(2000 + qk_i * 8 + 1, qk_i < 60);
-      issue_qk(qk_i);
+      issue_qk(qk_i, bars + 8 * (kMSFull + (qk_i & 1)));
       MLA_TRACE_AT(2000 + qk_i * 8 + 2, qk_i < 60);
       ++qk_i;
       progressed = true;
     }
-    if (pv_i < qk_i && mbar_test_wait(bars + 8 * (kMPFull + (pv_i & 1)), (pv_i >> 1) & 1)) {
+    auto try_pv = [&]() {
+      if (pv_i < qk_i && mbar_test_wait(bars + 8 * (kMPFull + (pv_i & 1)), (pv_i >> 1) & 1)) {
+        tc_fence_after_sync();
+        MLA_TRACE_AT(2000 + pv_i * 8 + 3, pv_i < 60);
+        issue_pv(pv_i);
+        MLA_TRACE_AT(2000 + pv_i * 8 + 4, pv_i < 60);
+        ++pv_i;
+        progressed = true;
+      }
+    };
+    try_pv();
+    // The softmax warps rewrote rows of the tile they hold (saturated e4m3-fnuz codes): its scores once more.
+    // They hold the oldest tile without P V; the P of the tile before it is complete by now, but this thread may
+    // not have seen it yet, hence the second look.
+    if (mbar_test_wait(bars + 8 * kMRedoReq, redos & 1)) {
+      try_pv();
       tc_fence_after_sync();
-      MLA_TRACE_AT(2000 + pv_i * 8 + 3, pv_i < 60);
-      issue_pv(pv_i);
-      MLA_TRACE_AT(2000 + pv_i * 8 + 4, pv_i < 60);
-      ++pv_i;
+      issue_qk(pv_i, bars + 8 * kMRedoDone);
+      ++redos;
       progressed = true;
     }
     if (progressed) {
@@ -441,6 +389,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   for (int r = 0; r < R; ++r) m_ref[r] = 0.f, l_sum[r] = 0.f;
   uint32_t slow = 0;          // exact-maximum rounds so far (phase of their barrier)
   uint32_t n_sat_rounds = 0;  // tiles with saturated entries so far (phase of their barrier)
+  uint32_t redos = 0;         // Q K^T repetitions so far (phase of their barriers)
 
   for (int j = 0; j < n; ++j) {
     const int buf = j & 1, par = (j >> 1) & 1;
@@ -452,29 +401,28 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     uint32_t d[N];
     tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
     const int tok_abs = (w.tile0 + j) * kTok + tl;
-    // Saturated e4m3-fnuz entries of this tile (the check warps listed them): the tensor core saw +-448 where
-    // the cache says +-480 (in e4m3 units); add the rest of this thread's token by hand, into the first term.
     const int st = j % kStagesMla;
-    // The count was written before the check warps passed the tile on; the MMA thread waited for that before
-    // it issued the Q K^T whose completion this thread has just waited for.  e4m3 caches have no such entries.
-    const int n_sat = p.kv_format != 0 ? 0 : min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
     const uint32_t* sat = reinterpret_cast<const uint32_t*>(smem + C::kOffSat) + st * kSatCap;
-    if (n_sat > 0) {
-      for (int e = 0; e < n_sat; ++e) {
-        const uint32_t ent = sat[e];
-        if (static_cast<int>(ent & 127u) != tl) continue;
-        const uint32_t col = (ent >> 7) & 1023u;
-        const float rest = (ent >> 17) ? -kSatResidual : kSatResidual;
-        const uint8_t* qt = smem + C::kOffQT + (col >> 7) * (N * 128);
+    // e4m3-fnuz: a byte 0x7F / 0xFF (+-240 there, NaN to the tensor core) in this thread's token row shows as NaN
+    // scores of the token.
+    bool tok_nan = false;
+    if (p.use_tma && tl < kTok && tok_abs >= w.end_max) {
+      // Box loads bring whole rows, also those between the end of what this CTA may see and the end of the slab:
+      // another position's tokens, or bytes nobody wrote.  Their scores are masked below, but P V would multiply
+      // p = 0 with whatever NaN code they hold: zero the row (the 16-byte copies of a pool do that themselves).
+      uint8_t* tile = smem + C::kOffKV + st * kTileBytesMla;
+#pragma unroll 4
+      for (uint32_t col0 = 0; col0 < kRowBytes; col0 += 16)
+        *reinterpret_cast<uint4*>(tile + (col0 >> 7) * kChunkBytes + swz128(tl, col0 & 127u)) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (p.kv_format == 0 && tl < kTok && tok_abs < w.end_max) {
 #pragma unroll
-        for (int r = 0; r < R; r += 2) {  // the two terms of rows r and r + 1 at this column
-          const float2 a = from_e4m3x2(qt[swz128(r, col & 127u)] | (qt[swz128(r + 1, col & 127u)] << 8));
-          const float2 b = from_e4m3x2(qt[swz128(R + r, col & 127u)] | (qt[swz128(R + r + 1, col & 127u)] << 8));
-          d[r] = __float_as_uint(__uint_as_float(d[r]) + rest * (a.x + b.x));
-          d[r + 1] = __float_as_uint(__uint_as_float(d[r + 1]) + rest * (a.y + b.y));
-        }
+      for (int r = 0; r < R; ++r) {
+        const float v = __uint_as_float(d[r]) + __uint_as_float(d[R + r]);
+        tok_nan = tok_nan || (v != v);
       }
     }
+    int n_sat = 0;
     float s[R];
     float over = -INFINITY;
     float scale_r[R];  // four 16-byte loads instead of sixteen scalar ones: shared-memory instructions are what this loop waits for
@@ -492,14 +440,74 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       over = fmaxf(over, s[r] - m_ref[r]);
     }
     const bool warp_over = __any_sync(0xffffffffu, over > kTauMla) || j == 0;
+    const bool warp_nan = __any_sync(0xffffffffu, tok_nan);
     if (lane == 0) {
-      flags[buf * 4 + warp] = warp_over ? 1 : 0;
+      flags[buf * 4 + warp] = (warp_over ? 1 : 0) | (warp_nan ? 2 : 0);
       mbar_arrive(bars + 8 * (kMFlag + buf));
     }
     MLA_TRACE_AT(j * 8 + 2, tr);
     MA_WAIT_WARP(bars + 8 * (kMFlag + buf), par, 0x71);
     MLA_TRACE_AT(j * 8 + 3, tr);
-    if ((flags[buf * 4 + 0] | flags[buf * 4 + 1] | flags[buf * 4 + 2] | flags[buf * 4 + 3]) != 0) {
+    int tile_flags = flags[buf * 4 + 0] | flags[buf * 4 + 1] | flags[buf * 4 + 2] | flags[buf * 4 + 3];
+    if (tile_flags & 2) {  // uniform over the CTA
+      // Rewrite the two codes one down (+-224) in the rows that showed NaN, list the entries for the corrections
+      // by hand, and have the MMA thread run the tile's Q K^T again on the rewritten bytes.
+      if (tok_nan) {
+        int* sat_cnt = reinterpret_cast<int*>(smem + C::kOffSatCnt) + st;
+        uint32_t* sat_w = reinterpret_cast<uint32_t*>(smem + C::kOffSat) + st * kSatCap;
+        uint8_t* tile = smem + C::kOffKV + st * kTileBytesMla;
+        for (int piece = 0; piece < kRowBytes / 16; ++piece) {
+          const uint32_t col0 = piece * 16;
+          uint4* ptr = reinterpret_cast<uint4*>(tile + (col0 >> 7) * kChunkBytes + swz128(tl, col0 & 127u));
+          uint4 v = *ptr;
+          uint32_t* x = reinterpret_cast<uint32_t*>(&v);
+          bool any = false;
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t hit = ((x[k] & 0x7F7F7F7Fu) + 0x01010101u) & 0x80808080u;
+            if (hit == 0u) continue;
+            any = true;
+            for (int b = 0; b < 4; ++b) {
+              if (((hit >> (8 * b)) & 0x80u) == 0u) continue;
+              const int slot = atomicAdd(sat_cnt, 1);
+              if (slot < kSatCap) sat_w[slot] = tl | ((col0 + k * 4 + b) << 7) | (((x[k] >> (8 * b + 7)) & 1u) << 17);
+            }
+            x[k] -= hit >> 7;
+          }
+          if (any) *ptr = v;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + 8 * kMRedoReq);
+      MA_WAIT_WARP(bars + 8 * kMRedoDone, redos & 1, 0x7A);
+      ++redos;
+      tc_fence_after_sync();
+      tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
+      n_sat = min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
+      // the tensor core saw +-448 where the cache says +-480 (in e4m3 units): add the rest of this token by hand
+      for (int e = 0; e < n_sat; ++e) {
+        const uint32_t ent = sat[e];
+        if (static_cast<int>(ent & 127u) != tl) continue;
+        const uint32_t col = (ent >> 7) & 1023u;
+        const float rest = (ent >> 17) ? -kSatResidual : kSatResidual;
+        const uint8_t* qt = smem + C::kOffQT + (col >> 7) * (N * 128);
+#pragma unroll
+        for (int r = 0; r < R; r += 2) {  // the two terms of rows r and r + 1 at this column
+          const float2 a = from_e4m3x2(qt[swz128(r, col & 127u)] | (qt[swz128(r + 1, col & 127u)] << 8));
+          const float2 b = from_e4m3x2(qt[swz128(R + r, col & 127u)] | (qt[swz128(R + r + 1, col & 127u)] << 8));
+          d[r] = __float_as_uint(__uint_as_float(d[r]) + rest * (a.x + b.x));
+          d[r + 1] = __float_as_uint(__uint_as_float(d[r + 1]) + rest * (a.y + b.y));
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
+        const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * scale_r[r];
+        s[r] = (tl < kTok && tok_abs < limit) ? v : -INFINITY;
+      }
+      tile_flags |= 1;  // the maxima were judged on NaN: take the exact path
+    }
+    if ((tile_flags & 1) != 0) {
       // exact row maxima of the tile: redux within the warp, shared memory across the four warps
       const int sb = slow & 1;
 #pragma unroll
@@ -735,10 +743,9 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
     const uint32_t bars = base + C::kOffBars;
     for (uint32_t i = 0; i < kMNumBars; ++i) {
       uint32_t count = 1;
-      if (i >= kMTileFull && i < kMTileFull + kStagesMla) count = kCheckThreads;
       if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
       if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
-      if (i >= kMMx && i < kMNumBars) count = 4;
+      if (i >= kMMx && i < kMNumBars && i != kMRedoDone) count = 4;
       mbar_init(bars + 8 * i, count);
     }
     abort_flag_s = 0;
@@ -754,10 +761,10 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   MLA_TRACE_AT(5001, tid == 0);
-  constexpr int kFirstCopyWarp = 5, kFirstCheckWarp = 5 + kCopyThreads / 32;
+  constexpr int kFirstCopyWarp = 5;
 
-  // The copy warps start fetching at once; the other nine warps first turn the query rows into Q^T.
-  if (warp >= kFirstCopyWarp && warp < kFirstCheckWarp) {
+  // The copy warps start fetching at once; the other five warps first turn the query rows into Q^T.
+  if (warp >= kFirstCopyWarp) {
     role_copy<kPos, kTma>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
   } else {
     // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a
@@ -768,9 +775,9 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
     float* row_scale = reinterpret_cast<float*>(smem + C::kOffRowScale);
     uint8_t* qt = smem + C::kOffQT;
     const float fmt = p.kv_format == 0 ? 2.f : 1.f;  // e4m3-fnuz bytes read as e4m3 are twice their value
-    constexpr int kPrepWarps = kThreadsMla / 32 - kCopyThreads / 32;  // 9
-    const int prep_warp = warp < kFirstCopyWarp ? warp : warp - kCopyThreads / 32;
-    constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 2: a warp takes rows prep_warp and prep_warp + 9
+    constexpr int kPrepWarps = kFirstCopyWarp;
+    const int prep_warp = warp;
+    constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + 5, + 10, + 15
     float2 vin[kRounds][9];  // 576 / 64: lane holds columns 64 i + 2 lane, + 1; all loads are issued before any is used
 #pragma unroll
     for (int k = 0; k < kRounds; ++k) {
@@ -819,15 +826,13 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
       }
     }
     fence_proxy_async_smem();
-    // every one of these nine warps gets here unconditionally: a plain named barrier is safe
+    // every one of these five warps gets here unconditionally: a plain named barrier is safe
     asm volatile("bar.sync 1, %0;" ::"n"(kPrepWarps * 32) : "memory");
     MLA_TRACE_AT(5002, tid == 0);
     if (warp < 4) {
       role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
     } else if (warp == 4) {
-      if (lane == 0) role_mma<kPos>(w, smem, base, tmem, ctx);
-    } else {
-      role_check<kPos, kTma>(p, w, base, smem, tid - kFirstCheckWarp * 32, ctx);
+      if (lane == 0) role_mma<kPos, kTma>(w, smem, base, tmem, ctx);
     }
   }
   tc_fence_before_sync();

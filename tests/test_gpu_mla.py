@@ -217,6 +217,38 @@ def test_saturated_fnuz_codes_are_corrected(ma, cuda_device, paged, density, exa
     assert err < (REL_L2 if exact else 0.1), err
 
 
+def test_saturated_codes_under_zero_query_columns(ma, cuda_device):
+    """Saturated codes whose query column is zero in every head change no score, but still reach the output
+    through V (latent columns) or not at all (rope columns)."""
+    B, S, H = 2, 700, 16
+    kv = _rand_kv(B, S, cuda_device, 41)
+    raw = kv.view(torch.uint8)
+    raw[:, ::7, 100] = 0x7F
+    raw[:, 3::11, 300] = 0xFF
+    raw[:, 5::13, 530] = 0x7F      # a rope column
+    lens = [S, 333]
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 41)
+    q_lat[..., 100] = 0
+    q_lat[..., 300] = 0
+    q_pe[..., 530 - LAT] = 0
+    kv_scale = 1.0 / 512.0
+    pool, kv_indices, kv_indptr = _paged_pool(kv, lens, cuda_device, 41)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+    ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens_t, None, kv_indices, kv_indptr, 2, SCALE, kv_scale)
+    out = o_lat.float().cpu().numpy().reshape(B, 1, H, LAT)
+    assert ma.last_status()[0] == 0 and np.isfinite(out).all()
+    qa, qb = q_lat.unsqueeze(1).float().cpu().numpy(), q_pe.unsqueeze(1).float().cpu().numpy()
+    err = mo.rel_l2(out, mo.mla_decode(qa, qb, raw.cpu().numpy(), lens, SCALE, kv_scale))
+    assert err < REL_L2, err
+    # the contiguous form reads whole slabs: request 0 only
+    o2 = torch.zeros_like(o_lat[:1])
+    ma.mla_decode_a16w8(q_lat[:1].contiguous(), q_pe[:1].contiguous(), kv[:1].contiguous(), o2, SCALE, kv_scale)
+    assert ma.last_status()[0] == 0
+    err = mo.rel_l2(o2.float().cpu().numpy().reshape(1, 1, H, LAT),
+                    mo.mla_decode(qa[:1], qb[:1], raw[:1].cpu().numpy(), [S], SCALE, kv_scale))
+    assert err < REL_L2, err
+
+
 def test_contiguous_argument_errors(ma, cuda_device):
     kv = _rand_kv(2, 256, cuda_device, 83)
     q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
