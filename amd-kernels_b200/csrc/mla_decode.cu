@@ -71,18 +71,18 @@ struct Cfg {
   static constexpr uint32_t kOffBars = kOffSat + kStagesMla * kSatCap * 4;
 };
 enum MlaBar : uint32_t {
-  kMTileEmpty = 3,  // [3] MMA -> copy warps
-  kMTileRaw = 6,    // [3] copy warps -> MMA: the tile has landed (256 copy threads, or 1 + bytes for box loads)
-  kMSFull = 9,      // [2] MMA -> softmax
-  kMPFull = 11,     // [2] softmax -> MMA (128 arrivals)
-  kMPvDone = 13,    // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
-  kMMx = 15,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
-  kMFlag = 17,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
-  kMEpi = 19,       //     softmax warps among themselves: denominators written (4 arrivals)
-  kMSat = 20,       // [2] softmax warps among themselves: P^T written, before a saturation correction (4 arrivals)
-  kMRedoReq = 22,   //     softmax warps -> MMA: rows of the oldest tile were rewritten, run its Q K^T again (4 arrivals)
-  kMRedoDone = 23,  //     MMA -> softmax: that Q K^T has completed
-  kMNumBars = 24
+  kMTileEmpty = 0,  // [3] MMA -> copy warps
+  kMTileRaw = 3,    // [3] copy warps -> MMA: the tile has landed (256 copy threads, or 1 + bytes for box loads)
+  kMSFull = 6,      // [2] MMA -> softmax
+  kMPFull = 8,     // [2] softmax -> MMA (128 arrivals)
+  kMPvDone = 10,    // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
+  kMMx = 12,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
+  kMFlag = 14,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
+  kMEpi = 16,       //     softmax warps among themselves: denominators written (4 arrivals)
+  kMSat = 17,       // [2] softmax warps among themselves: P^T written, before a saturation correction (4 arrivals)
+  kMRedoReq = 19,   //     softmax warps -> MMA: rows of the oldest tile were rewritten, run its Q K^T again (4 arrivals)
+  kMRedoDone = 20,  //     MMA -> softmax: that Q K^T has completed
+  kMNumBars = 21
 };
 
 #ifdef MA_TRACE
@@ -675,8 +675,6 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   __syncwarp();
   if (lane == 0) mbar_arrive(bars + 8 * kMEpi);
   MA_WAIT_WARP(bars + 8 * kMEpi, 0, 0x76);
-  MA_WAIT_WARP(bars + 8 * (kMPvDone + ((n - 1) & 1)), ((n - 1) >> 1) & 1, 0x74);
-  tc_fence_after_sync();
   const float fmt = p.kv_format == 0 ? 2.f : 1.f;
   float inv[R];  // per row: kv_scale / (format factor x denominator); 0 for a row without tokens
   bool live[R];
@@ -695,6 +693,9 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       live[r + q] = row_live(r + q);
     }
   }
+  // (all of the above ran while the last P V was still at work)
+  MA_WAIT_WARP(bars + 8 * (kMPvDone + ((n - 1) & 1)), ((n - 1) >> 1) & 1, 0x74);
+  tc_fence_after_sync();
 #pragma unroll 1
   for (int mt = 0; mt < 4; ++mt) {
     uint32_t o[N];
@@ -738,18 +739,45 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   const WaitCtx ctx{p.status, abort_flag};
   const Work w = decode_work(p, kPos);
   MLA_TRACE_AT(5000, tid == 0);
+#ifdef MA_TRACE
+  if (tid == 0 && blockIdx.x < 1024) g_trace_mla[6000 + blockIdx.x] = globaltimer_ns();
+#endif
 
-  if (tid == 0) {
-    const uint32_t bars = base + C::kOffBars;
-    for (uint32_t i = 0; i < kMNumBars; ++i) {
-      uint32_t count = 1;
-      if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
-      if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
-      if (i >= kMMx && i < kMNumBars && i != kMRedoDone) count = 4;
-      mbar_init(bars + 8 * i, count);
+  // The query rows are fetched first of all, before any KV copy is on its way: behind three tiles of every CTA
+  // (25 MB on the whole GPU) these few loads would wait for microseconds.
+  constexpr int kFirstCopyWarp = 5;
+  const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
+  const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
+  constexpr int kPrepWarps = kFirstCopyWarp;
+  const int prep_warp = warp;
+  constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + 5, + 10, + 15
+  // A row is 72 pieces of 8 elements (16 bytes): a lane takes pieces lane, lane + 32 and (lanes 0-7) lane + 64.
+  // All loads are issued before any is used.
+  uint4 vin[kRounds][3];
+#pragma unroll
+  for (int k = 0; k < kRounds; ++k) {
+    const int r = prep_warp + k * kPrepWarps;
+    const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
+    const bool live = warp < kFirstCopyWarp && r < R && h < w.heads && pos < w.q_len;
+    const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+      const int x = (i * 32 + lane) * 8;
+      vin[k][i] = make_uint4(0u, 0u, 0u, 0u);
+      if (live && x < kRowBytes)
+        vin[k][i] = x < kLat ? *reinterpret_cast<const uint4*>(q_lat + qrow * kLat + x)
+                             : *reinterpret_cast<const uint4*>(q_pe + qrow * 64 + (x - kLat));
     }
-    abort_flag_s = 0;
-    for (int i = 0; i < 4; ++i) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
+  }
+  if (tid < static_cast<int>(kMNumBars)) {  // one barrier per thread
+    const uint32_t i = tid;
+    uint32_t count = 1;
+    if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
+    if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
+    if (i >= kMMx && i < kMNumBars && i != kMRedoDone) count = 4;
+    mbar_init(base + C::kOffBars + 8 * i, count);
+    if (i == 0) abort_flag_s = 0;
+    if (i < 4) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
     mbar_fence_init();
   }
   if (warp == 4) {
@@ -761,7 +789,12 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   MLA_TRACE_AT(5001, tid == 0);
-  constexpr int kFirstCopyWarp = 5;
+  // The query data is first looked at from here on (keeps the compiler from waiting for it above the barrier).
+#pragma unroll
+  for (int k = 0; k < kRounds; ++k)
+#pragma unroll
+    for (int i = 0; i < 3; ++i)
+      asm volatile("" : "+r"(vin[k][i].x), "+r"(vin[k][i].y), "+r"(vin[k][i].z), "+r"(vin[k][i].w));
 
   // The copy warps start fetching at once; the other five warps first turn the query rows into Q^T.
   if (warp >= kFirstCopyWarp) {
@@ -770,40 +803,25 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
     // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a
     // row is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
     // q * f = q1 + q2 exact for every element within 2^-7 of the largest (8 significant bits = 4 + 4).
-    const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
-    const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
     float* row_scale = reinterpret_cast<float*>(smem + C::kOffRowScale);
     uint8_t* qt = smem + C::kOffQT;
     const float fmt = p.kv_format == 0 ? 2.f : 1.f;  // e4m3-fnuz bytes read as e4m3 are twice their value
-    constexpr int kPrepWarps = kFirstCopyWarp;
-    const int prep_warp = warp;
-    constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + 5, + 10, + 15
-    float2 vin[kRounds][9];  // 576 / 64: lane holds columns 64 i + 2 lane, + 1; all loads are issued before any is used
-#pragma unroll
-    for (int k = 0; k < kRounds; ++k) {
-      const int r = prep_warp + k * kPrepWarps;
-      const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
-      const bool live = r < R && h < w.heads && pos < w.q_len;
-      const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
-#pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const int x = i * 64 + lane * 2;
-        vin[k][i] = make_float2(0.f, 0.f);
-        if (live) {
-          const __nv_bfloat162 two = x < kLat ? *reinterpret_cast<const __nv_bfloat162*>(q_lat + qrow * kLat + x)
-                                              : *reinterpret_cast<const __nv_bfloat162*>(q_pe + qrow * 64 + (x - kLat));
-          vin[k][i] = __bfloat1622float2(two);
-        }
-      }
-    }
 #pragma unroll
     for (int k = 0; k < kRounds; ++k) {
       const int r = prep_warp + k * kPrepWarps;
       if (r >= R) break;
-      const float2* v = vin[k];
+      float v[3][8];
       float amax = 0.f;
 #pragma unroll
-      for (int i = 0; i < 9; ++i) amax = fmaxf(amax, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
+      for (int i = 0; i < 3; ++i) {
+        const uint32_t in[4] = {vin[k][i].x, vin[k][i].y, vin[k][i].z, vin[k][i].w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 two = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&in[q]));
+          v[i][2 * q] = two.x, v[i][2 * q + 1] = two.y;
+          amax = fmaxf(amax, fmaxf(fabsf(two.x), fabsf(two.y)));
+        }
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
       // f = 2^(7 - exponent(amax)); NaN / inf / zero rows keep f = 1
@@ -814,15 +832,22 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
       }
       if (lane == 0) row_scale[r] = p.scale * 1.4426950408889634f * p.kv_scale / (fmt * f);
 #pragma unroll
-      for (int i = 0; i < 9; ++i) {
-        const float a = v[i].x * f, b = v[i].y * f;
-        const uint32_t t1 = to_e4m3x2(a, b);
-        const float2 back = from_e4m3x2(t1);
-        const uint32_t t2 = to_e4m3x2(a - back.x, b - back.y);
-        const uint32_t x = i * 64 + lane * 2;
-        const uint32_t chunk = x >> 7, col = x & 127u;  // two adjacent bytes of one 16-byte piece
-        *reinterpret_cast<uint16_t*>(qt + chunk * (N * 128) + swz128(r, col)) = static_cast<uint16_t>(t1);
-        *reinterpret_cast<uint16_t*>(qt + chunk * (N * 128) + swz128(R + r, col)) = static_cast<uint16_t>(t2);
+      for (int i = 0; i < 3; ++i) {
+        const uint32_t x = (i * 32 + lane) * 8;
+        if (x >= kRowBytes) break;
+        uint32_t t1[4], t2[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float a = v[i][2 * q] * f, b = v[i][2 * q + 1] * f;
+          t1[q] = to_e4m3x2(a, b);
+          const float2 back = from_e4m3x2(t1[q]);
+          t2[q] = to_e4m3x2(a - back.x, b - back.y);
+        }
+        const uint32_t chunk = x >> 7, col = x & 127u;  // eight adjacent bytes of one 16-byte piece
+        *reinterpret_cast<uint2*>(qt + chunk * (N * 128) + swz128(r, col)) =
+            make_uint2(t1[0] | (t1[1] << 16), t1[2] | (t1[3] << 16));
+        *reinterpret_cast<uint2*>(qt + chunk * (N * 128) + swz128(R + r, col)) =
+            make_uint2(t2[0] | (t2[1] << 16), t2[2] | (t2[3] << 16));
       }
     }
     fence_proxy_async_smem();
@@ -838,6 +863,9 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem, C::kTmemCols);
+#ifdef MA_TRACE
+  if (tid == 0 && blockIdx.x < 1024) g_trace_mla[7000 + blockIdx.x] = globaltimer_ns();
+#endif
 }
 
 // ---------------------------------------------------------------------------
