@@ -739,6 +739,7 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   const WaitCtx ctx{p.status, abort_flag};
   const Work w = decode_work(p, kPos);
   MLA_TRACE_AT(5000, tid == 0);
+  if (p.parts > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // mla_merge_kernel may line up
 #ifdef MA_TRACE
   if (tid == 0 && blockIdx.x < 1024) g_trace_mla[6000 + blockIdx.x] = globaltimer_ns();
 #endif
@@ -871,34 +872,56 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
 // ---------------------------------------------------------------------------
 // merge of the KV parts: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, scaled back, rounded to bf16
 // ---------------------------------------------------------------------------
+// One CTA per (output row, quarter of the 512 dimensions); its four warps take every fourth part, a lane four
+// dimensions (16-byte loads), and the warps' sums meet in shared memory.
 __global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int kpos) {
   const int R = kHeadsMax * kpos;
-  const int row = blockIdx.x;  // (b, pos, h)
+  const int row = blockIdx.x >> 2, quarter = blockIdx.x & 3;  // row = (b, pos, h)
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = row % p.heads, pos = (row / p.heads) % p.q_len, b = row / (p.heads * p.q_len);
   const int brow = p.rows != nullptr ? p.rows[b] : b;
   const int group = pos / kpos, r = (pos % kpos) * kHeadsMax + h;
   const size_t slot0 = (static_cast<size_t>(b) * p.groups + group) * p.parts;
   const float2* ml = reinterpret_cast<const float2*>(p.part_ml);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the decode grid has completed and its partials are visible
+  auto live = [](float2 v) { return v.y > 0.f || v.y != v.y; };  // a part without tokens has denominator 0
   float m_all = -INFINITY;
-  for (int q = 0; q < p.parts; ++q) {
+  for (int q = lane; q < p.parts; q += 32) {
     const float2 v = ml[(slot0 + q) * R + r];
-    if (v.y > 0.f || v.y != v.y) m_all = fmaxf(m_all, v.x);
+    if (live(v)) m_all = fmaxf(m_all, v.x);
   }
-  float acc[4] = {0.f, 0.f, 0.f, 0.f}, l_all = 0.f;
-  for (int q = 0; q < p.parts; ++q) {
-    const float2 v = ml[(slot0 + q) * R + r];
-    if (!(v.y > 0.f || v.y != v.y)) continue;  // a part without tokens
-    const float wgt = ex2_approx(v.x - m_all);
-    l_all += wgt * v.y;
-    const float* o = p.part_o + ((slot0 + q) * R + r) * kLat;
 #pragma unroll
-    for (int k = 0; k < 4; ++k) acc[k] += wgt * o[k * 128 + threadIdx.x];
+  for (int o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float l_all = 0.f;
+#pragma unroll 4
+  for (int q = warp; q < p.parts; q += 4) {
+    const float2 v = ml[(slot0 + q) * R + r];
+    const bool on = live(v);
+    const float wgt = on ? ex2_approx(v.x - m_all) : 0.f;
+    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (on) o = *reinterpret_cast<const float4*>(p.part_o + ((slot0 + q) * R + r) * kLat + quarter * 128 + lane * 4);
+    l_all += wgt * v.y;
+    acc.x += wgt * o.x, acc.y += wgt * o.y, acc.z += wgt * o.z, acc.w += wgt * o.w;
+  }
+  __shared__ float4 acc_s[4][32];
+  __shared__ float l_s[4];
+  acc_s[warp][lane] = acc;
+  if (lane == 0) l_s[warp] = l_all;
+  __syncthreads();
+  if (warp != 0) return;
+  l_all = (l_s[0] + l_s[1]) + (l_s[2] + l_s[3]);
+#pragma unroll
+  for (int k = 1; k < 4; ++k) {
+    const float4 x = acc_s[k][lane];
+    acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
   }
   const float fmt = p.kv_format == 0 ? 2.f : 1.f;
   const float inv = l_all > 0.f || l_all != l_all ? p.kv_scale / (fmt * l_all) : 0.f;
-  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat) + ((static_cast<size_t>(brow) * p.q_len + pos) * p.heads + h) * kLat;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) out[k * 128 + threadIdx.x] = __float2bfloat16_rn(acc[k] * inv);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat) +
+                       ((static_cast<size_t>(brow) * p.q_len + pos) * p.heads + h) * kLat + quarter * 128 + lane * 4;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
 }
 
 template <int kPos, bool kTma>
@@ -912,8 +935,15 @@ cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
   mla_decode_kernel<kPos, kTma><<<p.batch * p.groups * p.parts, block_threads(kTma), smem_bytes, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.parts == 1) return e;  // a single part writes the final output itself
-  mla_merge_kernel<<<p.batch * p.q_len * p.heads, 128, 0, stream>>>(p, kPos);
-  return cudaGetLastError();
+  // The merge is launched as a programmatic dependent: its CTAs may take their places while the parts still
+  // run (they are small enough to sit beside a decode CTA) and wait there for the decode grid to complete.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.batch * p.q_len * p.heads * 4), cfg.blockDim = dim3(128), cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, mla_merge_kernel, p, static_cast<int>(kPos));
 }
 
 }  // namespace

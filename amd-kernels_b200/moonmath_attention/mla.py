@@ -32,7 +32,7 @@ __all__ = [
 _LAT, _ROPE = 512, 64
 _QK = _LAT + _ROPE
 _KV_FORMAT = {torch.float8_e4m3fnuz: 0, torch.float8_e4m3fn: 1}
-_MAX_PARTS = 64  # MA_MLA_MAX_PARTS
+_MAX_PARTS = 256  # MA_MLA_MAX_PARTS
 
 
 def _check_q(q_lat, q_pe, o_lat, who: str, multiq: bool) -> int:

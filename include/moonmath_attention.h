@@ -204,7 +204,7 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
  *     request, +-224 for the surplus.  0x80 (NaN in fnuz) reads as zero.
  *   parts: KV split per request, 1..MA_MLA_MAX_PARTS (ma_mla_plan_parts); workspace: ma_mla_workspace_bytes.
  */
-#define MA_MLA_MAX_PARTS 64
+#define MA_MLA_MAX_PARTS 256
 int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts);
 int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,

@@ -169,7 +169,7 @@ def test_single_query_ragged_lengths_and_few_heads(ma, cuda_device, B, H, S):
 
 
 @pytest.mark.parametrize("q_len", [1, 2, 3, 6, 7])
-@pytest.mark.parametrize("parts", [1, 3, 64])
+@pytest.mark.parametrize("parts", [1, 3, 64, 256])
 def test_paged_every_window_length_and_split(ma, cuda_device, q_len, parts):
     B, H = 2, 16
     seq_lens = [700, 1301]

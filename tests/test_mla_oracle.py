@@ -50,7 +50,8 @@ def test_planner_fills_the_gpu_once_and_keeps_parts_long():
     assert plan(148, 1, 4096) == 1 and plan(300, 1, 4096) == 1
     assert plan(32, 1, 8192) == 4                # 148 // 32, 16 parts of four tiles available
     assert plan(16, 4, 8192) == 2                # a window of four positions is four CTAs per part
-    assert plan(1, 1, 131072) == 64              # capped by MA_MLA_MAX_PARTS
+    assert plan(1, 1, 131072) == 148             # one long request still fills the GPU
+    assert plan(1, 1, 131072 * 4) == 148
     assert plan(1, 1, 1000) == 2                 # 8 tiles: at least four tiles per part
     assert plan(1, 1, 100) == 1
     assert plan(0, 1, 100) == 1 and plan(1, 9, 100) == 1
@@ -66,7 +67,7 @@ def test_mla_argument_validation_return_codes():
     assert call(B=0) == 1 and call(H=17) == 1 and call(H=0) == 1
     assert call(q_len=0) == 2 and call(q_len=9) == 2
     assert call(S=0) == 5 and call(idx=16) == 5          # paged needs kv_indptr and seq_lens
-    assert call(parts=0) == 18 and call(parts=65) == 18 and call(fmt=2) == 18
+    assert call(parts=0) == 18 and call(parts=257) == 18 and call(fmt=2) == 18
     assert call(q=None) == 9 and call(q=8) == 10
     assert call() == 11                                    # workspace is required
     assert b"parts" in _abi.lib.ma_error_string(18)
