@@ -872,9 +872,10 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
 // ---------------------------------------------------------------------------
 // merge of the KV parts: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, scaled back, rounded to bf16
 // ---------------------------------------------------------------------------
-// One CTA per (output row, quarter of the 512 dimensions); its four warps take every fourth part, a lane four
+// One CTA per (output row, quarter of the 512 dimensions); its eight warps take every eighth part, a lane four
 // dimensions (16-byte loads), and the warps' sums meet in shared memory.
-__global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int kpos) {
+constexpr int kMergeWarps = 8;
+__global__ void __launch_bounds__(kMergeWarps * 32) mla_merge_kernel(const MlaParams p, int kpos) {
   const int R = kHeadsMax * kpos;
   const int row = blockIdx.x >> 2, quarter = blockIdx.x & 3;  // row = (b, pos, h)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -895,7 +896,7 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int k
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float l_all = 0.f;
 #pragma unroll 4
-  for (int q = warp; q < p.parts; q += 4) {
+  for (int q = warp; q < p.parts; q += kMergeWarps) {
     const float2 v = ml[(slot0 + q) * R + r];
     const bool on = live(v);
     const float wgt = on ? ex2_approx(v.x - m_all) : 0.f;
@@ -904,17 +905,17 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const MlaParams p, int k
     l_all += wgt * v.y;
     acc.x += wgt * o.x, acc.y += wgt * o.y, acc.z += wgt * o.z, acc.w += wgt * o.w;
   }
-  __shared__ float4 acc_s[4][32];
-  __shared__ float l_s[4];
+  __shared__ float4 acc_s[kMergeWarps][32];
+  __shared__ float l_s[kMergeWarps];
   acc_s[warp][lane] = acc;
   if (lane == 0) l_s[warp] = l_all;
   __syncthreads();
   if (warp != 0) return;
-  l_all = (l_s[0] + l_s[1]) + (l_s[2] + l_s[3]);
 #pragma unroll
-  for (int k = 1; k < 4; ++k) {
+  for (int k = 1; k < kMergeWarps; ++k) {
     const float4 x = acc_s[k][lane];
     acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
+    l_all += l_s[k];
   }
   const float fmt = p.kv_format == 0 ? 2.f : 1.f;
   const float inv = l_all > 0.f || l_all != l_all ? p.kv_scale / (fmt * l_all) : 0.f;
@@ -938,7 +939,7 @@ cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
   // The merge is launched as a programmatic dependent: its CTAs may take their places while the parts still
   // run (they are small enough to sit beside a decode CTA) and wait there for the decode grid to complete.
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.batch * p.q_len * p.heads * 4), cfg.blockDim = dim3(128), cfg.stream = stream;
+  cfg.gridDim = dim3(p.batch * p.q_len * p.heads * 4), cfg.blockDim = dim3(kMergeWarps * 32), cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;

@@ -210,7 +210,7 @@ def run_reference(args, rank: int, world: int) -> None:
 # 16 heads, e4m3-fnuz cache as the reference stores it.  HBM-bound: every 576-byte row is read once.
 MLA_SHAPE = {"batch": 148, "seq": 4096, "heads": 16}
 # dram__bytes_read.sum + dram__bytes_write.sum of one mla_decode_kernel launch at that shape (profiles/mla_decode_b200.md)
-MLA_NCU_TRAFFIC_BYTES = 351978752 + 4113664
+MLA_NCU_TRAFFIC_BYTES = 352050688 + 4211968
 
 
 def mla_cpu_oracle_rate(budget_s: float) -> dict:
@@ -232,7 +232,7 @@ def mla_cpu_oracle_rate(budget_s: float) -> dict:
         n += 1
     dt = time.perf_counter() - t0
     return {"value": n * S * 576 / dt / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{n} requests of {S} cached tokens (of the workload's {MLA_SHAPE['batch']}), numpy oracle, {dt:.1f} s"}
+            "sample": f"{n} decode steps of one request of {S} cached tokens (the workload has {MLA_SHAPE['batch']}), numpy oracle, {dt:.1f} s"}
 
 
 def run_mla(args) -> None:
