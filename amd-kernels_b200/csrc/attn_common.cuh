@@ -68,7 +68,7 @@ struct LiteParams {
 
 // MLA absorbed-decode launch (mla_decode.cu).
 struct MlaParams {
-  CUtensorMap tm_kv;      // contiguous slab only: rank-3 byte map {576, seq, batch}, box 128 bytes x 96 rows, 128-byte swizzle
+  CUtensorMap tm_kv, tm_kv_rope;      // contiguous slab only: rank-3 byte map {576, seq, batch}, box 128 bytes x 96 rows, 128-byte swizzle
   int use_tma;            // 1: tiles come by box loads through tm_kv; 0: by 16-byte asynchronous copies (paged pool)
   const void* q_lat;      // bf16 [B, q_len, H, 512]  ([B, H, 512] when q_len = 1)
   const void* q_pe;       // bf16 [B, q_len, H, 64]

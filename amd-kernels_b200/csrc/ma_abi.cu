@@ -56,16 +56,18 @@ int make_tensor_map(CUtensorMap* tm, const void* ptr, int batch, int heads, int 
 
 // Rank-3 byte map over a contiguous MLA cache slab [batch][seq][576]: box = one 128-byte column chunk of 96 token
 // rows; rows past `seq` and bytes past 576 read as zeros.
-int make_kv_slab_map(CUtensorMap* tm, const void* ptr, int batch, int seq) {
+// Box of `width` byte columns x 96 token rows of a [batch][seq][576 B] slab; 128 wide under the 128-byte swizzle
+// (latent chunks), 64 wide under the 64-byte swizzle (rope chunk).
+int make_kv_slab_map(CUtensorMap* tm, const void* ptr, int batch, int seq, int width) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return MA_ERR_DRIVER;
   const cuuint64_t dims[3] = {576, static_cast<cuuint64_t>(seq), static_cast<cuuint64_t>(batch)};
   const cuuint64_t strides[2] = {576, static_cast<cuuint64_t>(576) * seq};
-  const cuuint32_t box[3] = {128, 96, 1};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(width), 96, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   const CUresult r = fn(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, elem,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, width == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? MA_OK : MA_ERR_TENSOR_MAP;
 }
 
@@ -355,21 +357,22 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
 
 // ---- MLA absorbed decode -------------------------------------------------------------------------------
 namespace {
-// Draft positions per CTA.  One: a window of q_len positions is q_len CTAs per (request, KV part) that read
-// the same KV rows, the later ones from L2 (the reference's q_len = 1 kernel does the same,
-// csrc/mla_decode_a16w8.hip "QLC=1").  The kernel template also takes two, but its softmax then keeps twice
-// the per-row state in registers and measured slower.
-int mla_pos_per_cta(int) { return 1; }
+// Draft positions per CTA.  Paged pools: one; a window of q_len positions is q_len CTAs per (request, KV part)
+// that read the same rows, the later ones from L2 (the reference's q_len = 1 kernel does the same,
+// csrc/mla_decode_a16w8.hip "QLC=1").  Contiguous slabs: two (a second group of softmax warps on the same tiles);
+// MA_MLA_POS1=1 is a development switch back to one.
+int mla_pos_per_cta(int q_len, bool slab) { return slab && q_len >= 2 && std::getenv("MA_MLA_POS1") == nullptr ? 2 : 1; }
 // Development switch: MA_MLA_NO_TMA=1 sends a contiguous slab through the copy path of the paged pool.
 bool flags_env_no_tma() { return std::getenv("MA_MLA_NO_TMA") != nullptr; }
-int mla_groups(int q_len) { return (q_len + mla_pos_per_cta(q_len) - 1) / mla_pos_per_cta(q_len); }
+int mla_groups(int q_len, int per) { return (q_len + per - 1) / per; }
 }  // namespace
 
-int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms) {
+namespace {
+int mla_plan(int batch, int q_len, int max_seq_len, int num_sms, bool slab) {
   if (batch <= 0 || q_len < 1 || q_len > 8 || max_seq_len <= 0) return 1;
   const int sms = resolve_sms(num_sms);
   if (sms <= 0) return 1;
-  const int base = batch * mla_groups(q_len);             // CTAs before any split
+  const int base = batch * mla_groups(q_len, mla_pos_per_cta(q_len, slab));  // CTAs before any split
   const int tiles = (max_seq_len + 127) / 128;            // 128-token tiles of the longest request
   int parts = sms / base;                                 // fill the GPU once ...
   const int by_length = (tiles + 3) / 4;                  // ... with at least four tiles (512 tokens) per part
@@ -377,12 +380,21 @@ int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms) {
   if (parts > MA_MLA_MAX_PARTS) parts = MA_MLA_MAX_PARTS;
   return parts < 1 ? 1 : parts;
 }
+}  // namespace
+
+int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms) {
+  return mla_plan(batch, q_len, max_seq_len, num_sms, false);
+}
+int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms) {
+  return mla_plan(batch, q_len, seq_len, num_sms, !flags_env_no_tma());
+}
 
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts) {
   if (batch <= 0 || q_len < 1 || q_len > 8 || parts < 1) return ma::kStatusBytes;
-  const size_t slots = static_cast<size_t>(batch) * mla_groups(q_len) * parts;
-  const size_t rows = 16u * mla_pos_per_cta(q_len);
-  return ma::kStatusBytes + slots * rows * (512 + 2) * sizeof(float);
+  // one slot of 16 rows per (request, position, part); positions are rounded up to even, which also covers
+  // CTAs that take two positions (32 rows per slot)
+  const size_t slots = static_cast<size_t>(batch) * (q_len == 1 ? 1 : (q_len + 1) / 2 * 2) * parts;
+  return ma::kStatusBytes + slots * 16u * (512 + 2) * sizeof(float);
 }
 
 int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
@@ -413,10 +425,12 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
   p.q_lat = q_lat, p.q_pe = q_pe, p.kv = kv, p.o_lat = o_lat;
   p.seq_lens = seq_lens, p.rows = rows, p.kv_indices = kv_indices, p.kv_indptr = kv_indptr;
   p.batch = batch, p.heads = heads, p.q_len = q_len, p.seq = seq_len;
-  p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len), p.groups = mla_groups(q_len);
+  const bool slab = !paged && !flags_env_no_tma();
+  p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len, slab), p.groups = mla_groups(q_len, p.pos_per_cta);
   p.kv_format = kv_format, p.scale = scale, p.kv_scale = kv_scale;
-  if (!paged && !(flags_env_no_tma())) {
-    const int rc = make_kv_slab_map(&p.tm_kv, kv, batch, seq_len);
+  if (slab) {
+    int rc = make_kv_slab_map(&p.tm_kv, kv, batch, seq_len, 128);
+    if (rc == MA_OK) rc = make_kv_slab_map(&p.tm_kv_rope, kv, batch, seq_len, 64);
     if (rc != MA_OK) return rc;
     p.use_tma = 1;
   }

@@ -40,18 +40,18 @@ using namespace sm100;
 constexpr int kLat = 512, kRowBytes = 576;
 constexpr int kTok = 96;                         // tokens per tile
 constexpr int kMmaM = 128;                       // rows of an MMA; S^T rows 96..127 are never looked at (see role_mma)
-constexpr int kChunks = 5;                       // 128-byte column chunks of a row: 4 latent + rope (64 bytes used)
-constexpr int kChunkBytes = kTok * 128;          // 12 KiB
-constexpr int kTileBytesMla = kChunks * kChunkBytes;
-constexpr int kStagesMla = 3;                    // a tile spends about as long being loaded as being used
+constexpr int kChunks = 5;                       // column chunks of a row: 4 latent of 128 bytes + rope of 64
+constexpr int kChunkBytes = kTok * 128;          // 12 KiB: a latent chunk, [96 rows][128 B], 128-byte swizzle
+constexpr int kRopeBytes = kTok * 64;            //  6 KiB: the rope chunk, [96 rows][64 B], 64-byte swizzle
+constexpr int kTileBytesMla = 4 * kChunkBytes + kRopeBytes;  // 55296 = 96 x 576: nothing is padded
+constexpr int kMaxStagesMla = 3;                 // a tile spends about as long being loaded as being used
 constexpr int kHeadsMax = 16;
-constexpr int kSoftmaxThreads = 128;
+constexpr int kSoftmaxThreads = 128;             // per draft position of the CTA
 // Copy warps: eight for the 16-byte copies of a paged pool, one (one thread of it) for box loads; the block is
 // launched with as many threads as its roles need, so the box-load variant has twice the registers per thread.
 constexpr int copy_threads(bool tma) { return tma ? 32 : 256; }
-constexpr int block_threads(bool tma) { return kSoftmaxThreads + 32 + copy_threads(tma); }  // 192 / 416
+constexpr int block_threads(bool tma, int pos) { return pos * kSoftmaxThreads + 32 + copy_threads(tma); }  // 192 / 416; two positions: 320
 constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
-constexpr int kSatCap = 640;                     // saturated e4m3-fnuz entries of one tile that are corrected exactly
 constexpr float kSatResidual = 32.f;             // +-240 fnuz = +-480 as e4m3; the tensor core gets +-448; the rest by hand
 
 template <int kPos>
@@ -59,30 +59,32 @@ struct Cfg {
   static constexpr int kRows = kHeadsMax * kPos;  // query rows per CTA
   static constexpr int kN = 2 * kRows;            // two e4m3 terms per row
   static constexpr uint32_t kTmemCols = kPos == 1 ? 256 : 512;  // S x 2 + O^T x 4 = 6 * kN = 192 / 384
+  static constexpr int kStages = 3;
+  static constexpr int kSatCap = kPos == 1 ? 640 : 256;         // saturated e4m3-fnuz entries of one tile that are corrected exactly
   static constexpr uint32_t kOffKV = 0;
-  static constexpr uint32_t kOffQT = kStagesMla * kTileBytesMla;       // [5 chunks][kN rows][128 B]
-  static constexpr uint32_t kOffPT = kOffQT + kChunks * kN * 128;      // [2][kN rows][128 B]
+  static constexpr uint32_t kOffQT = kStages * kTileBytesMla;       // [5 chunks][kN rows][128 B]
+  static constexpr uint32_t kOffPT = kOffQT + kChunks * kN * 128;      // [2][128 token rows][kN B], kN-byte swizzle (96 rows used)
   static constexpr uint32_t kOffRowScale = kOffPT + 2 * kN * 128;      // float [kRows]: score = (S1 + S2) * this
   static constexpr uint32_t kOffMx = kOffRowScale + kRows * 4;         // float [2][4 warps][kRows]
   static constexpr uint32_t kOffL = kOffMx + 2 * 4 * kRows * 4;        // float [4 warps][kRows]: denominators (epilogue)
-  static constexpr uint32_t kOffFlags = kOffL + 4 * kRows * 4;         // int [2][4 warps]
-  static constexpr uint32_t kOffSatCnt = kOffFlags + 2 * 4 * 4;        // int [kStagesMla]: saturated entries of the tile in a stage; [3]: first P V accumulates
-  static constexpr uint32_t kOffSat = kOffSatCnt + 16;                 // uint32 [kStagesMla][kSatCap]: token | column << 7 | negative << 17
-  static constexpr uint32_t kOffBars = kOffSat + kStagesMla * kSatCap * 4;
+  static constexpr uint32_t kOffFlags = kOffL + 4 * kRows * 4;         // int [2][4 kPos softmax warps]
+  static constexpr uint32_t kOffSatCnt = kOffFlags + 2 * 4 * kPos * 4; // int [kStages]: saturated entries of the tile in a stage; [3]: first P V accumulates
+  static constexpr uint32_t kOffSat = kOffSatCnt + 16;                 // uint32 [kStages][kSatCap]: token | column << 7 | negative << 17
+  static constexpr uint32_t kOffBars = kOffSat + kStages * kSatCap * 4;
 };
 enum MlaBar : uint32_t {
   kMTileEmpty = 0,  // [3] MMA -> copy warps
   kMTileRaw = 3,    // [3] copy warps -> MMA: the tile has landed (256 copy threads, or 1 + bytes for box loads)
   kMSFull = 6,      // [2] MMA -> softmax
-  kMPFull = 8,     // [2] softmax -> MMA (128 arrivals)
+  kMPFull = 8,      // [2] softmax -> MMA (every softmax thread arrives)
   kMPvDone = 10,    // [2] MMA -> softmax: P V of the tile complete (P buffer free, O stable)
-  kMMx = 12,        // [2] softmax warps among themselves: row maxima written (4 arrivals)
-  kMFlag = 14,      // [2] softmax warps among themselves: overflow flags written (4 arrivals)
-  kMEpi = 16,       //     softmax warps among themselves: denominators written (4 arrivals)
-  kMSat = 17,       // [2] softmax warps among themselves: P^T written, before a saturation correction (4 arrivals)
-  kMRedoReq = 19,   //     softmax warps -> MMA: rows of the oldest tile were rewritten, run its Q K^T again (4 arrivals)
-  kMRedoDone = 20,  //     MMA -> softmax: that Q K^T has completed
-  kMNumBars = 21
+  kMMx = 12,        // [2][2 groups] softmax warps of a group among themselves: row maxima written (4 arrivals)
+  kMFlag = 16,      // [2] all softmax warps: overflow and NaN flags written (one arrival per warp)
+  kMEpi = 18,       // [2 groups] softmax warps of a group: denominators written (4 arrivals)
+  kMSat = 20,       // [2] all softmax warps: P^T written, before a saturation correction (one arrival per warp)
+  kMRedoReq = 22,   //     softmax warps -> MMA: rows of the oldest tile were rewritten, run its Q K^T again (one arrival per warp)
+  kMRedoDone = 23,  //     MMA -> softmax: that Q K^T has completed
+  kMNumBars = 24
 };
 
 #ifdef MA_TRACE
@@ -130,6 +132,24 @@ __device__ __forceinline__ float2 from_e4m3x2(uint32_t v) {
 // Byte offset of (row, byte column) inside a [rows][128 B] block with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t col) {
   return row * 128u + ((((col >> 4) ^ (row & 7u)) << 4) | (col & 15u));
+}
+// The same for a [rows][64 B] block with the 64-byte swizzle (16-byte pieces xor-ed with bits 1-2 of the row).
+__device__ __forceinline__ uint32_t swz64(uint32_t row, uint32_t col) {
+  return row * 64u + ((((col >> 4) ^ ((row >> 1) & 3u)) << 4) | (col & 15u));
+}
+// P of a tile is stored token-major, [tokens][N bytes] under the N-byte swizzle (N = 32 or 64), so that a
+// softmax thread (one token) writes its probabilities with 16-byte stores; the tensor core reads it as an
+// MN-major B operand.  Byte offset of (token, accumulator column n):
+template <int N>
+__device__ __forceinline__ uint32_t p_off(uint32_t tok, uint32_t n) {
+  static_assert(N == 32 || N == 64, "one swizzle row per token");
+  const uint32_t x = N == 32 ? (tok >> 2) & 1u : (tok >> 1) & 3u;
+  return tok * N + ((((n >> 4) ^ x) << 4) | (n & 15u));
+}
+// Byte offset of (token row, byte column 0..575) inside a KV tile.
+__device__ __forceinline__ uint32_t kv_off(uint32_t row, uint32_t col) {
+  return col < static_cast<uint32_t>(kLat) ? (col >> 7) * kChunkBytes + swz128(row, col & 127u)
+                                           : 4u * kChunkBytes + swz64(row, col - kLat);
 }
 
 struct Work {
@@ -182,18 +202,19 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
   constexpr int kCopyThreads = copy_threads(kTma);
   const uint32_t bars = base + C::kOffBars;
   if constexpr (kTma) {
-    // Contiguous slab: five box loads per tile (one per 128-byte column chunk, 96 rows each), issued by one
+    // Contiguous slab: five box loads per tile (one per column chunk, 96 rows each), issued by one
     // thread.  Rows past the slab and the columns past byte 576 of the rope chunk arrive as zeros.
     if (lt != 0) return;
     for (int j = 0; j < w.tiles; ++j) {
-      const int st = j % kStagesMla;
-      if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / kStagesMla) - 1) & 1, 0x50);
+      const int st = j % C::kStages;
+      if (j >= C::kStages) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / C::kStages) - 1) & 1, 0x50);
       MLA_TRACE_AT(4000 + j * 4 + 0, j < 60);
       const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
       const uint32_t bar = bars + 8 * (kMTileRaw + st);
       mbar_arrive_expect_tx(bar, kTileBytesMla);
 #pragma unroll
-      for (int c = 0; c < kChunks; ++c) tma_load_3d(tile + c * kChunkBytes, &p.tm_kv, bar, c * 128, (w.tile0 + j) * kTok, w.b);
+      for (int c = 0; c < 4; ++c) tma_load_3d(tile + c * kChunkBytes, &p.tm_kv, bar, c * 128, (w.tile0 + j) * kTok, w.b);
+      tma_load_3d(tile + 4 * kChunkBytes, &p.tm_kv_rope, bar, kLat, (w.tile0 + j) * kTok, w.b);
       MLA_TRACE_AT(4000 + j * 4 + 1, j < 60);
     }
     return;
@@ -214,10 +235,10 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
   };
   long long slot_next = slot_of(0);
   for (int j = 0; j < w.tiles; ++j) {
-    const int st = j % kStagesMla;
+    const int st = j % C::kStages;
     const long long slot_mine = slot_next;
     slot_next = slot_of(j + 1);
-    if (j >= kStagesMla) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / kStagesMla) - 1) & 1, 0x50);
+    if (j >= C::kStages) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / C::kStages) - 1) & 1, 0x50);
     MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
     const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
 #pragma unroll
@@ -228,7 +249,7 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
       if (piece < kPiecesPerWarp) {
         const uint32_t tok = warp * kRowsPerWarp + row, col = static_cast<uint32_t>(q) * 16u;
         // rows past the end are zero-filled (source size 0)
-        cp_async16(tile + (col >> 7) * kChunkBytes + swz128(tok, col & 127u),
+        cp_async16(tile + kv_off(tok, col),
                    kv + (slot < 0 ? 0 : slot) * kRowBytes + col, slot < 0 ? 0u : 16u);
       }
     }
@@ -236,6 +257,16 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
   }
   }
+}
+
+__device__ __forceinline__ uint64_t make_desc_hi(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+// Shared-memory descriptor of a K-major operand stored as [rows][64 B] under the 64-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc_sw64(uint32_t lo) {
+  return make_desc_hi(lo, (512u >> 4) | (1u << 14) | (4u << 29));  // SBO = 8 rows x 64 B, version 1, swizzle mode 64 B
 }
 
 // ---------------------------------------------------------------------------
@@ -246,7 +277,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
   using C = Cfg<kPos>;
   constexpr uint32_t kFmtE4M3 = 0;
   constexpr uint32_t idesc_qk = umma_idesc(kFmtE4M3, kFmtE4M3, 0, 0, kMmaM, C::kN);
-  constexpr uint32_t idesc_pv = umma_idesc(kFmtE4M3, kFmtE4M3, 1, 0, kMmaM, C::kN);
+  constexpr uint32_t idesc_pv = umma_idesc(kFmtE4M3, kFmtE4M3, 1, 1, kMmaM, C::kN);
   const uint32_t bars = base + C::kOffBars;
   const uint32_t qt_lo = desc_lo_kmajor(base + C::kOffQT);
   const int n = w.tiles;
@@ -254,35 +285,44 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
   // of whatever follows the chunk in shared memory.  A row of D depends on its own row of A only, so this
   // fills S^T rows 96..127 with numbers nobody reads.  P V has the tokens on K: three steps of 32, exact.
   auto issue_qk = [&](int j, uint32_t done_bar) {
-    const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
+    const uint32_t tile = base + C::kOffKV + (j % C::kStages) * kTileBytesMla;
     const uint32_t a_lo = desc_lo_kmajor(tile);
     const uint32_t d = tmem + (j & 1) * C::kN;
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
+    for (int c = 0; c < 4; ++c) {
 #pragma unroll
-      for (int ks = 0; ks < (c < 4 ? 4 : 2); ++ks) {
+      for (int ks = 0; ks < 4; ++ks) {
         umma_ss_f8(d, make_desc(a_lo + ((c * kChunkBytes + ks * 32) >> 4)),
                    make_desc(qt_lo + ((c * C::kN * 128 + ks * 32) >> 4)), idesc_qk, (c | ks) != 0 ? 1u : 0u);
       }
+    }
+    // the rope chunk: 64-byte rows under the 64-byte swizzle (8 rows = 512 bytes); Q^T keeps 128-byte rows
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      umma_ss_f8(d, make_desc_sw64(a_lo + ((4 * kChunkBytes + ks * 32) >> 4)),
+                 make_desc(qt_lo + ((4 * C::kN * 128 + ks * 32) >> 4)), idesc_qk, 1u);
     }
     umma_commit(done_bar);
   };
   auto issue_pv = [&](int j) {
     // a saturation correction may have put something into O^T before the first P V (role_softmax)
-    const bool keep = j > 0 || *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kStagesMla) != 0;
-    const uint32_t tile = base + C::kOffKV + (j % kStagesMla) * kTileBytesMla;
-    const uint32_t pt_lo = desc_lo_kmajor(base + C::kOffPT + (j & 1) * C::kN * 128);
+    const bool keep = j > 0 || *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kMaxStagesMla) != 0;
+    const uint32_t tile = base + C::kOffKV + (j % C::kStages) * kTileBytesMla;
+    // B = P, MN-major: rows of kN bytes per token, 8 tokens per swizzle atom, 32 tokens per step
+    constexpr uint32_t pt_hi = ((8u * C::kN) >> 4) | (1u << 14) | ((C::kN == 32 ? 6u : 4u) << 29);
+    const uint32_t pt_lo = (((base + C::kOffPT + (j & 1) * C::kN * 128) & 0x3FFFFu) >> 4) | (1u << 16);
 #pragma unroll
     for (int mt = 0; mt < 4; ++mt) {
       // A = 128 latent bytes of every token row (M), 32 token rows per step (K): MN-major, one swizzle atom wide
       const uint32_t a_lo = desc_lo_mnmajor<kTok>(tile + mt * kChunkBytes);
 #pragma unroll
       for (int ks = 0; ks < kTok / 32; ++ks) {
-        umma_ss_f8(tmem + (2 + mt) * C::kN, make_desc(a_lo + ((ks * 32 * 128) >> 4)), make_desc(pt_lo + ((ks * 32) >> 4)),
+        umma_ss_f8(tmem + (2 + mt) * C::kN, make_desc(a_lo + ((ks * 32 * 128) >> 4)),
+                   make_desc_hi(pt_lo + ((ks * 32 * C::kN) >> 4), pt_hi),
                    idesc_pv, (keep || ks > 0) ? 1u : 0u);
       }
     }
-    umma_commit(bars + 8 * (kMTileEmpty + (j % kStagesMla)));
+    umma_commit(bars + 8 * (kMTileEmpty + (j % C::kStages)));
     umma_commit(bars + 8 * (kMPvDone + (j & 1)));
   };
   // Whatever is ready is issued: Q K^T of tile i needs the tile and the S buffer (read out by the softmax of
@@ -294,7 +334,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
   while (pv_i < n) {
     bool progressed = false;
     if (qk_i < n && qk_i - pv_i < 2 &&
-        mbar_test_wait(bars + 8 * (kMTileRaw + (qk_i % kStagesMla)), (qk_i / kStagesMla) & 1)) {
+        mbar_test_wait(bars + 8 * (kMTileRaw + (qk_i % C::kStages)), (qk_i / C::kStages) & 1)) {
       if constexpr (!kTma) fence_proxy_async_smem();
       tc_fence_after_sync();
       MLA_TRACE_AT(2000 + qk_i * 8 + 1, qk_i < 60);
@@ -373,17 +413,38 @@ __device__ __forceinline__ void tmem_load_cols(uint32_t taddr, uint32_t (&d)[kCo
 // ---------------------------------------------------------------------------
 template <int kPos>
 __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, uint8_t* smem, uint32_t base,
-                                             uint32_t tmem, int tl, const WaitCtx& ctx) {
+                                             uint32_t tmem, int tid, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
-  constexpr int R = C::kRows, N = C::kN;
+  // A group of four warps owns one draft position: R = 16 query rows (heads), whose two e4m3 terms sit in
+  // accumulator columns [row0, row0 + 16) and [RT + row0, RT + row0 + 16) of S^T and of every O^T tile.
+  constexpr int R = kHeadsMax, RT = C::kRows, N = C::kN, kW = 4 * kPos;
+  const int group = tid >> 7, tl = tid & 127;
+  const int warp = tl >> 5, lane = tl & 31, gwarp = tid >> 5;
+  const uint32_t row0 = group * R;
   const uint32_t bars = base + C::kOffBars;
   const uint32_t lane_sel = static_cast<uint32_t>(tl & ~31) << 16;
-  const int warp = tl >> 5, lane = tl & 31;
-  const float* row_scale = reinterpret_cast<const float*>(smem + C::kOffRowScale);
-  float* mx = reinterpret_cast<float*>(smem + C::kOffMx);          // [2][4][R] row maxima of a tile, per warp
-  volatile int* flags = reinterpret_cast<volatile int*>(smem + C::kOffFlags);  // [2][4] "a score is above reference + tau"
-  float* l_part = reinterpret_cast<float*>(smem + C::kOffL);       // [4][R] per-warp denominators (epilogue)
+  const float* row_scale = reinterpret_cast<const float*>(smem + C::kOffRowScale) + row0;
+  float* mx = reinterpret_cast<float*>(smem + C::kOffMx);          // [2][groups][4][R] row maxima of a tile, per warp
+  volatile int* flags = reinterpret_cast<volatile int*>(smem + C::kOffFlags);  // [2][kW] bit 0: a score is above reference + tau; bit 1: NaN
+  float* l_part = reinterpret_cast<float*>(smem + C::kOffL) + group * 4 * R;  // [4][R] per-warp denominators (epilogue)
   const int n = w.tiles;
+  // tokens [0, limit) are visible to this group's position; a group past the window sees none and writes nothing
+  const bool pos_live = w.pos0 + group < w.q_len;
+  const int limit = pos_live ? w.len - w.q_len + w.pos0 + group + 1 : 0;
+  auto ld_pair = [&](uint32_t taddr, uint32_t (&r)[2 * R]) {  // taddr: column 0 of an N-column block
+    if constexpr (kPos == 1) {
+      tmem_ld32_sync(taddr, r);
+    } else {
+      tmem_ld16x2_sync(taddr + row0, taddr + RT + row0, r);
+    }
+  };
+  auto st_pair = [&](uint32_t taddr, const uint32_t (&r)[2 * R]) {
+    if constexpr (kPos == 1) {
+      tmem_st32(taddr, r);
+    } else {
+      tmem_st16x2(taddr + row0, taddr + RT + row0, r);
+    }
+  };
   float m_ref[R], l_sum[R];
 #pragma unroll
   for (int r = 0; r < R; ++r) m_ref[r] = 0.f, l_sum[r] = 0.f;
@@ -393,16 +454,16 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
 
   for (int j = 0; j < n; ++j) {
     const int buf = j & 1, par = (j >> 1) & 1;
-    const bool tr = tl == 0 && j < 60;
+    const bool tr = tid == 0 && j < 60;
     MLA_TRACE_AT(j * 8 + 0, tr);
     MA_WAIT_WARP(bars + 8 * (kMSFull + buf), par, 0x70);
     MLA_TRACE_AT(j * 8 + 1, tr);
     tc_fence_after_sync();
-    uint32_t d[N];
-    tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
+    uint32_t d[2 * R];
+    ld_pair(tmem + buf * N + lane_sel, d);
     const int tok_abs = (w.tile0 + j) * kTok + tl;
-    const int st = j % kStagesMla;
-    const uint32_t* sat = reinterpret_cast<const uint32_t*>(smem + C::kOffSat) + st * kSatCap;
+    const int st = j % C::kStages;
+    const uint32_t* sat = reinterpret_cast<const uint32_t*>(smem + C::kOffSat) + st * C::kSatCap;
     // e4m3-fnuz: a byte 0x7F / 0xFF (+-240 there, NaN to the tensor core) in this thread's token row shows as NaN
     // scores of the token.
     bool tok_nan = false;
@@ -413,9 +474,9 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       uint8_t* tile = smem + C::kOffKV + st * kTileBytesMla;
 #pragma unroll 4
       for (uint32_t col0 = 0; col0 < kRowBytes; col0 += 16)
-        *reinterpret_cast<uint4*>(tile + (col0 >> 7) * kChunkBytes + swz128(tl, col0 & 127u)) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(tile + kv_off(tl, col0)) = make_uint4(0u, 0u, 0u, 0u);
     }
-    if (p.kv_format == 0 && tl < kTok && tok_abs < w.end_max) {
+    if (p.kv_format == 0 && tl < kTok && tok_abs < limit) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const float v = __uint_as_float(d[r]) + __uint_as_float(d[R + r]);
@@ -433,8 +494,6 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-      // position (r / 16) of the group sees tokens [0, len - q_len + pos + 1)
-      const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
       const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * scale_r[r];
       s[r] = (tl < kTok && tok_abs < limit) ? v : -INFINITY;
       over = fmaxf(over, s[r] - m_ref[r]);
@@ -442,23 +501,27 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     const bool warp_over = __any_sync(0xffffffffu, over > kTauMla) || j == 0;
     const bool warp_nan = __any_sync(0xffffffffu, tok_nan);
     if (lane == 0) {
-      flags[buf * 4 + warp] = (warp_over ? 1 : 0) | (warp_nan ? 2 : 0);
+      flags[buf * kW + gwarp] = (warp_over ? 1 : 0) | (warp_nan ? 2 : 0);
       mbar_arrive(bars + 8 * (kMFlag + buf));
     }
     MLA_TRACE_AT(j * 8 + 2, tr);
     MA_WAIT_WARP(bars + 8 * (kMFlag + buf), par, 0x71);
     MLA_TRACE_AT(j * 8 + 3, tr);
-    int tile_flags = flags[buf * 4 + 0] | flags[buf * 4 + 1] | flags[buf * 4 + 2] | flags[buf * 4 + 3];
+    // overflow is this group's own business, a NaN (the tile is rewritten and multiplied again) everybody's
+    int tile_flags = 0;
+#pragma unroll
+    for (int k = 0; k < kW; ++k) tile_flags |= flags[buf * kW + k] & ((k >> 2) == group ? 3 : 2);
     if (tile_flags & 2) {  // uniform over the CTA
       // Rewrite the two codes one down (+-224) in the rows that showed NaN, list the entries for the corrections
       // by hand, and have the MMA thread run the tile's Q K^T again on the rewritten bytes.
-      if (tok_nan) {
+      // (a token that several positions see is rewritten by the first of them)
+      if (tok_nan && (group == 0 || tok_abs >= limit - group)) {
         int* sat_cnt = reinterpret_cast<int*>(smem + C::kOffSatCnt) + st;
-        uint32_t* sat_w = reinterpret_cast<uint32_t*>(smem + C::kOffSat) + st * kSatCap;
+        uint32_t* sat_w = reinterpret_cast<uint32_t*>(smem + C::kOffSat) + st * C::kSatCap;
         uint8_t* tile = smem + C::kOffKV + st * kTileBytesMla;
         for (int piece = 0; piece < kRowBytes / 16; ++piece) {
           const uint32_t col0 = piece * 16;
-          uint4* ptr = reinterpret_cast<uint4*>(tile + (col0 >> 7) * kChunkBytes + swz128(tl, col0 & 127u));
+          uint4* ptr = reinterpret_cast<uint4*>(tile + kv_off(tl, col0));
           uint4 v = *ptr;
           uint32_t* x = reinterpret_cast<uint32_t*>(&v);
           bool any = false;
@@ -469,7 +532,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
             for (int b = 0; b < 4; ++b) {
               if (((hit >> (8 * b)) & 0x80u) == 0u) continue;
               const int slot = atomicAdd(sat_cnt, 1);
-              if (slot < kSatCap) sat_w[slot] = tl | ((col0 + k * 4 + b) << 7) | (((x[k] >> (8 * b + 7)) & 1u) << 17);
+              if (slot < C::kSatCap) sat_w[slot] = tl | ((col0 + k * 4 + b) << 7) | (((x[k] >> (8 * b + 7)) & 1u) << 17);
             }
             x[k] -= hit >> 7;
           }
@@ -482,8 +545,8 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       MA_WAIT_WARP(bars + 8 * kMRedoDone, redos & 1, 0x7A);
       ++redos;
       tc_fence_after_sync();
-      tmem_load_cols<N>(tmem + buf * N + lane_sel, d);
-      n_sat = min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), kSatCap);
+      ld_pair(tmem + buf * N + lane_sel, d);
+      n_sat = min(*reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * st), C::kSatCap);
       // the tensor core saw +-448 where the cache says +-480 (in e4m3 units): add the rest of this token by hand
       for (int e = 0; e < n_sat; ++e) {
         const uint32_t ent = sat[e];
@@ -493,15 +556,14 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
         const uint8_t* qt = smem + C::kOffQT + (col >> 7) * (N * 128);
 #pragma unroll
         for (int r = 0; r < R; r += 2) {  // the two terms of rows r and r + 1 at this column
-          const float2 a = from_e4m3x2(qt[swz128(r, col & 127u)] | (qt[swz128(r + 1, col & 127u)] << 8));
-          const float2 b = from_e4m3x2(qt[swz128(R + r, col & 127u)] | (qt[swz128(R + r + 1, col & 127u)] << 8));
+          const float2 a = from_e4m3x2(qt[swz128(row0 + r, col & 127u)] | (qt[swz128(row0 + r + 1, col & 127u)] << 8));
+          const float2 b = from_e4m3x2(qt[swz128(RT + row0 + r, col & 127u)] | (qt[swz128(RT + row0 + r + 1, col & 127u)] << 8));
           d[r] = __float_as_uint(__uint_as_float(d[r]) + rest * (a.x + b.x));
           d[r + 1] = __float_as_uint(__uint_as_float(d[r + 1]) + rest * (a.y + b.y));
         }
       }
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const int limit = w.len - w.q_len + w.pos0 + (r / kHeadsMax) + 1;
         const float v = (__uint_as_float(d[r]) + __uint_as_float(d[R + r])) * scale_r[r];
         s[r] = (tl < kTok && tok_abs < limit) ? v : -INFINITY;
       }
@@ -513,17 +575,17 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int k = __reduce_max_sync(0xffffffffu, float_key(s[r]));
-        if (lane == (r & 31)) mx[(sb * 4 + warp) * R + r] = key_float(k);
+        if (lane == (r & 31)) mx[((sb * kPos + group) * 4 + warp) * R + r] = key_float(k);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bars + 8 * (kMMx + sb));
-      MA_WAIT_WARP(bars + 8 * (kMMx + sb), (slow >> 1) & 1, 0x75);
+      if (lane == 0) mbar_arrive(bars + 8 * (kMMx + sb + 2 * group));
+      MA_WAIT_WARP(bars + 8 * (kMMx + sb + 2 * group), (slow >> 1) & 1, 0x75);
       ++slow;
       float alpha[R];
       bool moved = false;
 #pragma unroll
       for (int r = 0; r < R; ++r) {
-        const float* m4 = mx + sb * 4 * R + r;
+        const float* m4 = mx + (sb * kPos + group) * 4 * R + r;
         const float m_tile = fmaxf(fmaxf(m4[0], m4[R]), fmaxf(m4[2 * R], m4[3 * R]));
         float m_new = m_ref[r];
         if (j == 0) {
@@ -541,16 +603,11 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
         tc_fence_after_sync();
 #pragma unroll 1
         for (int mt = 0; mt < 4; ++mt) {
-          uint32_t o[N];
-          tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
+          uint32_t o[2 * R];
+          ld_pair(tmem + (2 + mt) * N + lane_sel, o);
 #pragma unroll
-          for (int c = 0; c < N; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c % R]);
-          if constexpr (N == 32) {
-            tmem_st32(tmem + (2 + mt) * N + lane_sel, o);
-          } else {
-            tmem_st32_at<0>(tmem + (2 + mt) * N + lane_sel, o);
-            tmem_st32_at<32>(tmem + (2 + mt) * N + lane_sel + 32, o);
-          }
+          for (int c = 0; c < 2 * R; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha[c % R]);
+          st_pair(tmem + (2 + mt) * N + lane_sel, o);
         }
         tmem_st_wait();
         tc_fence_before_sync();
@@ -571,14 +628,11 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     if (j >= 2) MA_WAIT_WARP(bars + 8 * (kMPvDone + buf), ((j - 2) >> 1) & 1, 0x73);
     MLA_TRACE_AT(j * 8 + 5, tr);
     uint8_t* pt = smem + C::kOffPT + buf * N * 128;
-    if (tl < kTok) {
-#pragma unroll
-    for (int r = 0; r < R; r += 2) {
-      pt[swz128(r, tl)] = static_cast<uint8_t>(t1[r / 2] & 0xFF);
-      pt[swz128(r + 1, tl)] = static_cast<uint8_t>(t1[r / 2] >> 8);
-      pt[swz128(R + r, tl)] = static_cast<uint8_t>(t2[r / 2] & 0xFF);
-      pt[swz128(R + r + 1, tl)] = static_cast<uint8_t>(t2[r / 2] >> 8);
-    }
+    if (tl < kTok) {  // the token's 16 first terms and 16 second terms: two 16-byte stores
+      *reinterpret_cast<uint4*>(pt + p_off<N>(tl, row0)) =
+          make_uint4(t1[0] | (t1[1] << 16), t1[2] | (t1[3] << 16), t1[4] | (t1[5] << 16), t1[6] | (t1[7] << 16));
+      *reinterpret_cast<uint4*>(pt + p_off<N>(tl, RT + row0)) =
+          make_uint4(t2[0] | (t2[1] << 16), t2[2] | (t2[3] << 16), t2[4] | (t2[5] << 16), t2[6] | (t2[7] << 16));
     }
     if (n_sat > 0) {  // uniform over the CTA
       // O^T misses p * (+-32) for every listed entry with a latent column.  The entry's output dimension is a
@@ -594,20 +648,13 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       } else {
         // The first P V of a part normally overwrites O^T.  Start it from zero here and tell the MMA thread to
         // accumulate instead, so that the patches below survive.
-        uint32_t zero[N];
+        uint32_t zero[2 * R];
 #pragma unroll
-        for (int n = 0; n < N; ++n) zero[n] = 0u;
+        for (int c = 0; c < 2 * R; ++c) zero[c] = 0u;
 #pragma unroll 1
-        for (int mt = 0; mt < 4; ++mt) {
-          if constexpr (N == 32) {
-            tmem_st32(tmem + (2 + mt) * N + lane_sel, zero);
-          } else {
-            tmem_st32_at<0>(tmem + (2 + mt) * N + lane_sel, zero);
-            tmem_st32_at<32>(tmem + (2 + mt) * N + lane_sel + 32, zero);
-          }
-        }
+        for (int mt = 0; mt < 4; ++mt) st_pair(tmem + (2 + mt) * N + lane_sel, zero);
         tmem_st_wait();
-        if (tl == 0) *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kStagesMla) = 1;
+        if (tl == 0) *reinterpret_cast<volatile int*>(smem + C::kOffSatCnt + 4 * kMaxStagesMla) = 1;
       }
       for (int e = 0; e < n_sat; ++e) {
         const uint32_t ent = sat[e];
@@ -615,22 +662,18 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
         if (col >= static_cast<uint32_t>(kLat) || ((col >> 5) & 3u) != static_cast<uint32_t>(warp)) continue;  // warp-uniform
         const float rest = (ent >> 17) ? -kSatResidual : kSatResidual;
         const uint32_t taddr = tmem + (2 + (col >> 7)) * N + lane_sel;
-        uint32_t o[N];
-        tmem_load_cols<N>(taddr, o);
+        uint32_t o[2 * R];
+        ld_pair(taddr, o);
         if (static_cast<uint32_t>(lane) == (col & 31u)) {
 #pragma unroll
-          for (int n = 0; n < N; n += 2) {
-            const float2 pq = from_e4m3x2(pt[swz128(n, tok)] | (pt[swz128(n + 1, tok)] << 8));
-            o[n] = __float_as_uint(__uint_as_float(o[n]) + rest * pq.x);
-            o[n + 1] = __float_as_uint(__uint_as_float(o[n + 1]) + rest * pq.y);
+          for (int c = 0; c < 2 * R; c += 2) {
+            const uint32_t pcol = (c < R ? row0 : RT + row0 - R) + c;  // accumulator column c of this group within P
+            const float2 pq = from_e4m3x2(*reinterpret_cast<const uint16_t*>(pt + p_off<N>(tok, pcol)));
+            o[c] = __float_as_uint(__uint_as_float(o[c]) + rest * pq.x);
+            o[c + 1] = __float_as_uint(__uint_as_float(o[c + 1]) + rest * pq.y);
           }
         }
-        if constexpr (N == 32) {
-          tmem_st32(taddr, o);
-        } else {
-          tmem_st32_at<0>(taddr, o);
-          tmem_st32_at<32>(taddr + 32, o);
-        }
+        st_pair(taddr, o);
         tmem_st_wait();
       }
       tc_fence_before_sync();
@@ -642,18 +685,18 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     MLA_TRACE_AT(j * 8 + 6, tr);
   }
 
-  MLA_TRACE_AT(5003, tl == 0);
+  MLA_TRACE_AT(5003, tid == 0);
   // epilogue.  With one KV part the CTA finishes its rows itself (normalise, scale back, round to bf16); with
   // several it leaves un-normalised fp32 outputs, reference maxima and denominators for mla_merge_kernel.
   const size_t slot = blockIdx.x;
-  float* part_o = p.part_o + slot * (static_cast<size_t>(R) * kLat);
-  float2* part_ml = reinterpret_cast<float2*>(p.part_ml) + slot * R;
+  float* part_o = p.part_o + (slot * RT + row0) * kLat;  // this group's 16 rows of the CTA's slot
+  float2* part_ml = reinterpret_cast<float2*>(p.part_ml) + slot * RT + row0;
   const bool direct = p.parts == 1;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat);
-  auto out_row = [&](int r) {  // row r of this CTA: position pos0 + r / 16, head r % 16
-    return ((static_cast<size_t>(w.brow) * w.q_len + w.pos0 + r / kHeadsMax) * w.heads + (r % kHeadsMax)) * kLat;
+  auto out_row = [&](int r) {  // row r of this group: its position, head r
+    return ((static_cast<size_t>(w.brow) * w.q_len + w.pos0 + group) * w.heads + r) * kLat;
   };
-  auto row_live = [&](int r) { return (r % kHeadsMax) < w.heads && w.pos0 + r / kHeadsMax < w.q_len; };
+  auto row_live = [&](int r) { return r < w.heads && pos_live; };
   if (n == 0) {  // no token in range (an empty part, or a request without tokens)
     if (direct) {
       for (int r = 0; r < R; ++r)
@@ -673,8 +716,8 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     if (lane == (r & 31)) l_part[warp * R + r] = v;
   }
   __syncwarp();
-  if (lane == 0) mbar_arrive(bars + 8 * kMEpi);
-  MA_WAIT_WARP(bars + 8 * kMEpi, 0, 0x76);
+  if (lane == 0) mbar_arrive(bars + 8 * (kMEpi + group));
+  MA_WAIT_WARP(bars + 8 * (kMEpi + group), 0, 0x76);
   const float fmt = p.kv_format == 0 ? 2.f : 1.f;
   float inv[R];  // per row: kv_scale / (format factor x denominator); 0 for a row without tokens
   bool live[R];
@@ -698,14 +741,14 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   tc_fence_after_sync();
 #pragma unroll 1
   for (int mt = 0; mt < 4; ++mt) {
-    uint32_t o[N];
-    tmem_load_cols<N>(tmem + (2 + mt) * N + lane_sel, o);
+    uint32_t o[2 * R];
+    ld_pair(tmem + (2 + mt) * N + lane_sel, o);
     if (direct) {
       __nv_bfloat16* dst = out + out_row(0) + mt * 128 + tl;  // rows of one position are consecutive heads
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const float v = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
-        if (live[r]) dst[(static_cast<size_t>(r / kHeadsMax) * w.heads + (r % kHeadsMax)) * kLat] = __float2bfloat16_rn(v * inv[r]);
+        if (live[r]) dst[static_cast<size_t>(r) * kLat] = __float2bfloat16_rn(v * inv[r]);
       }
     } else {
 #pragma unroll
@@ -713,7 +756,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
         part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
     }
   }
-  MLA_TRACE_AT(5004, tl == 0);
+  MLA_TRACE_AT(5004, tid == 0);
   if (!direct && tl < R) {
     const float l = (l_part[tl] + l_part[R + tl]) + (l_part[2 * R + tl] + l_part[3 * R + tl]);
     float m = 0.f;
@@ -725,9 +768,9 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
 }
 
 template <int kPos, bool kTma>
-__global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
+__global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
   using C = Cfg<kPos>;
-  constexpr int kCopyThreads = copy_threads(kTma), kThreadsMla = block_threads(kTma);
+  constexpr int kCopyThreads = copy_threads(kTma);
   constexpr int R = C::kRows, N = C::kN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -746,12 +789,12 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
 
   // The query rows are fetched first of all, before any KV copy is on its way: behind three tiles of every CTA
   // (25 MB on the whole GPU) these few loads would wait for microseconds.
-  constexpr int kFirstCopyWarp = 5;
+  constexpr int kMmaWarp = 4 * kPos, kFirstCopyWarp = kMmaWarp + 1;  // softmax warps, MMA warp, copy warps
   const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
   const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
   constexpr int kPrepWarps = kFirstCopyWarp;
   const int prep_warp = warp;
-  constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + 5, + 10, + 15
+  constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + kPrepWarps, ...
   // A row is 72 pieces of 8 elements (16 bytes): a lane takes pieces lane, lane + 32 and (lanes 0-7) lane + 64.
   // All loads are issued before any is used.
   uint4 vin[kRounds][3];
@@ -773,15 +816,16 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
   if (tid < static_cast<int>(kMNumBars)) {  // one barrier per thread
     const uint32_t i = tid;
     uint32_t count = 1;
-    if (i >= kMTileRaw && i < kMTileRaw + kStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
-    if (i >= kMPFull && i < kMPFull + 2) count = kSoftmaxThreads;
-    if (i >= kMMx && i < kMNumBars && i != kMRedoDone) count = 4;
+    if (i >= kMTileRaw && i < kMTileRaw + kMaxStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
+    if (i >= kMPFull && i < kMPFull + 2) count = kPos * kSoftmaxThreads;
+    if ((i >= kMMx && i < kMMx + 4) || (i >= kMEpi && i < kMEpi + 2)) count = 4;
+    if ((i >= kMFlag && i < kMFlag + 2) || (i >= kMSat && i < kMSat + 2) || i == kMRedoReq) count = 4 * kPos;
     mbar_init(base + C::kOffBars + 8 * i, count);
     if (i == 0) abort_flag_s = 0;
     if (i < 4) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
     tmem_relinquish();
   }
@@ -797,7 +841,7 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
     for (int i = 0; i < 3; ++i)
       asm volatile("" : "+r"(vin[k][i].x), "+r"(vin[k][i].y), "+r"(vin[k][i].z), "+r"(vin[k][i].w));
 
-  // The copy warps start fetching at once; the other five warps first turn the query rows into Q^T.
+  // The copy warps start fetching at once; the other warps first turn the query rows into Q^T.
   if (warp >= kFirstCopyWarp) {
     role_copy<kPos, kTma>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
   } else {
@@ -852,18 +896,18 @@ __global__ void __launch_bounds__(block_threads(kTma), 1) mla_decode_kernel(cons
       }
     }
     fence_proxy_async_smem();
-    // every one of these five warps gets here unconditionally: a plain named barrier is safe
+    // every one of these warps gets here unconditionally: a plain named barrier is safe
     asm volatile("bar.sync 1, %0;" ::"n"(kPrepWarps * 32) : "memory");
     MLA_TRACE_AT(5002, tid == 0);
-    if (warp < 4) {
+    if (warp < kMmaWarp) {
       role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
-    } else if (warp == 4) {
+    } else if (warp == kMmaWarp) {
       if (lane == 0) role_mma<kPos, kTma>(w, smem, base, tmem, ctx);
     }
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) tmem_dealloc(tmem, C::kTmemCols);
+  if (warp == kMmaWarp) tmem_dealloc(tmem, C::kTmemCols);
 #ifdef MA_TRACE
   if (tid == 0 && blockIdx.x < 1024) g_trace_mla[7000 + blockIdx.x] = globaltimer_ns();
 #endif
@@ -933,7 +977,7 @@ cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel<kPos, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_bytes));
   if (e != cudaSuccess) return e;
-  mla_decode_kernel<kPos, kTma><<<p.batch * p.groups * p.parts, block_threads(kTma), smem_bytes, stream>>>(p);
+  mla_decode_kernel<kPos, kTma><<<p.batch * p.groups * p.parts, block_threads(kTma, kPos), smem_bytes, stream>>>(p);
   e = cudaGetLastError();
   if (e != cudaSuccess || p.parts == 1) return e;  // a single part writes the final output itself
   // The merge is launched as a programmatic dependent: its CTAs may take their places while the parts still
@@ -956,7 +1000,8 @@ extern "C" int ma_trace_read_mla(unsigned long long* host, int n) {
 #endif
 
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
-  if (p.pos_per_cta != 1) return cudaErrorInvalidValue;  // only the one-position instance is built
+  if (p.pos_per_cta == 2 && p.use_tma) return launch_one<2, true>(p, stream);
+  if (p.pos_per_cta != 1) return cudaErrorInvalidValue;
   return p.use_tma ? launch_one<1, true>(p, stream) : launch_one<1, false>(p, stream);
 }
 

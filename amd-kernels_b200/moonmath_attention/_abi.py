@@ -43,6 +43,7 @@ EXPORTS = (
     "ma_lite_tile",
     "ma_attention_forward_lite",
     "ma_mla_plan_parts",
+    "ma_mla_plan_parts_contiguous",
     "ma_mla_workspace_bytes",
     "ma_mla_decode_a16w8",
 )
@@ -87,6 +88,8 @@ def _load() -> ctypes.CDLL:
     )
     lib.ma_mla_plan_parts.restype = c_int
     lib.ma_mla_plan_parts.argtypes = [c_int] * 4
+    lib.ma_mla_plan_parts_contiguous.restype = c_int
+    lib.ma_mla_plan_parts_contiguous.argtypes = [c_int] * 4
     lib.ma_mla_workspace_bytes.restype = c_size_t
     lib.ma_mla_workspace_bytes.argtypes = [c_int] * 3
     lib.ma_mla_decode_a16w8.restype = c_int

@@ -109,7 +109,7 @@ def _contiguous(who, multiq, q_lat, q_pe, kv, o_lat, scale, kv_scale):
     if multiq and q_lat.size(0) > 32:
         raise ValueError(f"{who}: B must be in [1,32]")
     B, S = q_lat.size(0), kv.size(1)
-    parts = int(_abi.lib.ma_mla_plan_parts(B, q_len, S, 0))
+    parts = int(_abi.lib.ma_mla_plan_parts_contiguous(B, q_len, S, 0))
     _launch(who, q_lat, q_pe, kv, o_lat, None, None, None, None, q_len, S, parts, scale, kv_scale, fmt)
 
 

@@ -206,6 +206,8 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
  */
 #define MA_MLA_MAX_PARTS 256
 int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
+/* The same for a contiguous cache (kv_indices == NULL), where a CTA may take two draft positions of a window. */
+int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms);
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts);
 int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
                         const int* rows, const int* kv_indices, const int* kv_indptr, int batch, int heads, int q_len,
