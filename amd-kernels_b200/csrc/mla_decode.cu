@@ -233,6 +233,18 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     return p.kv_indices != nullptr ? static_cast<long long>(p.kv_indices[idx0 + tok_abs])
                                    : static_cast<long long>(w.b) * p.seq + tok_abs;
   };
+  // where this lane's pieces go and come from does not change from tile to tile
+  constexpr int kRoundsCopy = (kPiecesPerWarp + 31) / 32;  // 14
+  uint32_t dst_off[kRoundsCopy], src_col[kRoundsCopy];
+  int src_row[kRoundsCopy];
+#pragma unroll
+  for (int i = 0; i < kRoundsCopy; ++i) {
+    const int piece = i * 32 + lane;
+    const int row = piece / 36, q = piece % 36;  // row 12 only in the last, half-empty round
+    src_row[i] = row < kRowsPerWarp ? row : 0;
+    src_col[i] = static_cast<uint32_t>(q) * 16u;
+    dst_off[i] = kv_off(warp * kRowsPerWarp + src_row[i], src_col[i]);
+  }
   long long slot_next = slot_of(0);
   for (int j = 0; j < w.tiles; ++j) {
     const int st = j % C::kStages;
@@ -242,16 +254,11 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
     const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
 #pragma unroll
-    for (int i = 0; i < (kPiecesPerWarp + 31) / 32; ++i) {
-      const int piece = i * 32 + lane;
-      const int row = piece / 36, q = piece % 36;  // row 12 only in the last, half-empty round
-      const long long slot = __shfl_sync(0xffffffffu, slot_mine, row < kRowsPerWarp ? row : 0);
-      if (piece < kPiecesPerWarp) {
-        const uint32_t tok = warp * kRowsPerWarp + row, col = static_cast<uint32_t>(q) * 16u;
-        // rows past the end are zero-filled (source size 0)
-        cp_async16(tile + kv_off(tok, col),
-                   kv + (slot < 0 ? 0 : slot) * kRowBytes + col, slot < 0 ? 0u : 16u);
-      }
+    for (int i = 0; i < kRoundsCopy; ++i) {
+      const long long slot = __shfl_sync(0xffffffffu, slot_mine, src_row[i]);
+      // rows past the end are zero-filled (source size 0)
+      if (i * 32 + lane < kPiecesPerWarp)
+        cp_async16(tile + dst_off[i], kv + (slot < 0 ? 0 : slot) * kRowBytes + src_col[i], slot < 0 ? 0u : 16u);
     }
     cp_async_arrive(bars + 8 * (kMTileRaw + st));
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);

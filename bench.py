@@ -210,7 +210,7 @@ def run_reference(args, rank: int, world: int) -> None:
 # 16 heads, e4m3-fnuz cache as the reference stores it.  HBM-bound: every 576-byte row is read once.
 MLA_SHAPE = {"batch": 148, "seq": 4096, "heads": 16}
 # dram__bytes_read.sum + dram__bytes_write.sum of one mla_decode_kernel launch at that shape (profiles/mla_decode_b200.md)
-MLA_NCU_TRAFFIC_BYTES = 352050688 + 4211968
+MLA_NCU_TRAFFIC_BYTES = 352064000 + 3900416
 
 
 def mla_cpu_oracle_rate(budget_s: float) -> dict:

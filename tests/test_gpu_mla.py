@@ -217,6 +217,30 @@ def test_saturated_fnuz_codes_are_corrected(ma, cuda_device, paged, density, exa
     assert err < (REL_L2 if exact else 0.1), err
 
 
+@pytest.mark.parametrize("q_len", [4, 5])
+def test_saturated_codes_in_a_window_on_a_contiguous_cache(ma, cuda_device, q_len):
+    """Two draft positions share a CTA there: both must get the corrections, the rows are rewritten once, and the
+    positions' last tokens (seen by one of the two only) count too."""
+    B, S, H = 2, 1000, 16
+    kv = _rand_kv(B, S, cuda_device, 43)
+    raw = kv.view(torch.uint8)
+    g = torch.Generator().manual_seed(5)
+    hit = (torch.rand(raw.shape, generator=g) < 0.002).to(cuda_device)
+    sign = (torch.rand(raw.shape, generator=g) < 0.5).to(cuda_device)
+    raw[hit & sign] = 0x7F
+    raw[hit & ~sign] = 0xFF
+    raw[:, S - q_len:, 17] = 0x7F      # the tokens at the causal limits
+    raw[:, S - q_len:, 530] = 0xFF
+    kv_scale = 1.0 / 512.0
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 43)
+    ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, kv_scale)
+    out = o_lat.float().cpu().numpy()
+    assert ma.last_status()[0] == 0 and np.isfinite(out).all()
+    err = mo.rel_l2(out, mo.mla_decode(q_lat.float().cpu().numpy(), q_pe.float().cpu().numpy(), raw.cpu().numpy(),
+                                       [S] * B, SCALE, kv_scale))
+    assert err < REL_L2, err
+
+
 def test_saturated_codes_under_zero_query_columns(ma, cuda_device):
     """Saturated codes whose query column is zero in every head change no score, but still reach the output
     through V (latent columns) or not at all (rope columns)."""

@@ -55,6 +55,9 @@ def test_planner_fills_the_gpu_once_and_keeps_parts_long():
     assert plan(1, 1, 1000) == 2                 # 8 tiles: at least four tiles per part
     assert plan(1, 1, 100) == 1
     assert plan(0, 1, 100) == 1 and plan(1, 9, 100) == 1
+    slab = lambda B, q, S: _abi.lib.ma_mla_plan_parts_contiguous(B, q, S, 148)
+    assert slab(16, 4, 8192) == 4                # a contiguous cache: two positions per CTA, 32 CTAs before the split
+    assert slab(16, 5, 8192) == 3 and slab(148, 1, 4096) == 1 and slab(32, 1, 8192) == 4
     ws = _abi.lib.ma_mla_workspace_bytes
     assert ws(32, 1, 4) == 256 + 32 * 4 * 16 * 514 * 4
     assert ws(2, 8, 3) == 256 + 2 * 8 * 3 * 16 * 514 * 4
