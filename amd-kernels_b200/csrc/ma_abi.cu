@@ -357,11 +357,10 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
 
 // ---- MLA absorbed decode -------------------------------------------------------------------------------
 namespace {
-// Draft positions per CTA.  Paged pools: one; a window of q_len positions is q_len CTAs per (request, KV part)
-// that read the same rows, the later ones from L2 (the reference's q_len = 1 kernel does the same,
-// csrc/mla_decode_a16w8.hip "QLC=1").  Contiguous slabs: two (a second group of softmax warps on the same tiles);
-// MA_MLA_POS1=1 is a development switch back to one.
-int mla_pos_per_cta(int q_len, bool slab) { return slab && q_len >= 2 && std::getenv("MA_MLA_POS1") == nullptr ? 2 : 1; }
+// Draft positions per CTA: two for a window (a second group of softmax warps on the same tiles), the way the
+// reference's multi-query kernel keeps a window resident (csrc/mla_decode_a16w8_multiq.hip:722).  MA_MLA_POS1=1 is a
+// development switch back to one CTA per position.
+int mla_pos_per_cta(int q_len, bool) { return q_len >= 2 && std::getenv("MA_MLA_POS1") == nullptr ? 2 : 1; }
 // Development switch: MA_MLA_NO_TMA=1 sends a contiguous slab through the copy path of the paged pool.
 bool flags_env_no_tma() { return std::getenv("MA_MLA_NO_TMA") != nullptr; }
 int mla_groups(int q_len, int per) { return (q_len + per - 1) / per; }

@@ -49,8 +49,14 @@ constexpr int kHeadsMax = 16;
 constexpr int kSoftmaxThreads = 128;             // per draft position of the CTA
 // Copy warps: eight for the 16-byte copies of a paged pool, one (one thread of it) for box loads; the block is
 // launched with as many threads as its roles need, so the box-load variant has twice the registers per thread.
-constexpr int copy_threads(bool tma) { return tma ? 32 : 256; }
-constexpr int block_threads(bool tma, int pos) { return pos * kSoftmaxThreads + 32 + copy_threads(tma); }  // 192 / 416; two positions: 320
+constexpr int copy_threads(bool tma, int pos) { return tma ? 32 : (pos == 1 ? 256 : 192); }
+// slab: 192 threads (two positions: 320); pool: 416 (two positions: 480) rounded up to whole warpgroups = 512,
+// because the pool variants move registers between warpgroups (setmaxnreg) and every warpgroup that takes part
+// is complete; the padding warps do nothing.
+constexpr int block_threads(bool tma, int pos) {
+  const int used = pos * kSoftmaxThreads + 32 + copy_threads(tma, pos);
+  return tma ? used : (used + 127) / 128 * 128;
+}
 constexpr float kTauMla = 8.f;                   // lazy rescale: p <= 2^8 = 256 < 448
 constexpr float kSatResidual = 32.f;             // +-240 fnuz = +-480 as e4m3; the tensor core gets +-448; the rest by hand
 
@@ -199,7 +205,7 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
 template <int kPos, bool kTma>
 __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uint32_t base, int lt, const WaitCtx& ctx) {
   using C = Cfg<kPos>;
-  constexpr int kCopyThreads = copy_threads(kTma);
+  constexpr int kCopyThreads = copy_threads(kTma, kPos);
   const uint32_t bars = base + C::kOffBars;
   if constexpr (kTma) {
     // Contiguous slab: five box loads per tile (one per column chunk, 96 rows each), issued by one
@@ -219,14 +225,14 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     }
     return;
   } else {
-  // Paged pool (or a slab sent this way): a warp copies 12 whole token rows of the tile, 36 pieces of 16 bytes
-  // each.  Lane k < 12 holds the pool slot of the warp's k-th row, fetched one tile ahead, so that no copy
-  // waits for an index load of its own.
+  // Paged pool (or a slab sent this way): a warp copies 12 (or 16) whole token rows of the tile, 36 pieces of
+  // 16 bytes each.  Lane k < 12 holds the pool slot of the warp's k-th row, fetched one tile ahead, so that no
+  // copy waits for an index load of its own.
   const uint8_t* kv = static_cast<const uint8_t*>(p.kv);
   const int idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
   const int warp = lt >> 5, lane = lt & 31;
-  constexpr int kRowsPerWarp = kTok / (kCopyThreads / 32);  // 12
-  constexpr int kPiecesPerWarp = kRowsPerWarp * 36;         // 432 = 13.5 warp-wide copies
+  constexpr int kRowsPerWarp = kTok / (kCopyThreads / 32);  // 12 (eight warps) or 16 (six)
+  constexpr int kPiecesPerWarp = kRowsPerWarp * 36;         // 432 = 13.5 warp-wide copies, or 576 = 18
   auto slot_of = [&](int j) -> long long {  // slot of row `lane` of this warp in tile j; -1: past the end
     const int tok_abs = (w.tile0 + j) * kTok + warp * kRowsPerWarp + lane;
     if (lane >= kRowsPerWarp || j >= w.tiles || tok_abs >= w.end_max) return -1;
@@ -234,16 +240,13 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
                                    : static_cast<long long>(w.b) * p.seq + tok_abs;
   };
   // where this lane's pieces go and come from does not change from tile to tile
-  constexpr int kRoundsCopy = (kPiecesPerWarp + 31) / 32;  // 14
-  uint32_t dst_off[kRoundsCopy], src_col[kRoundsCopy];
-  int src_row[kRoundsCopy];
+  constexpr int kRoundsCopy = (kPiecesPerWarp + 31) / 32;  // 14 or 18
+  uint32_t dst_off[kRoundsCopy];
 #pragma unroll
   for (int i = 0; i < kRoundsCopy; ++i) {
     const int piece = i * 32 + lane;
-    const int row = piece / 36, q = piece % 36;  // row 12 only in the last, half-empty round
-    src_row[i] = row < kRowsPerWarp ? row : 0;
-    src_col[i] = static_cast<uint32_t>(q) * 16u;
-    dst_off[i] = kv_off(warp * kRowsPerWarp + src_row[i], src_col[i]);
+    const int row = piece / 36;  // row == kRowsPerWarp only in the last, half-empty round
+    dst_off[i] = kv_off(warp * kRowsPerWarp + (row < kRowsPerWarp ? row : 0), static_cast<uint32_t>(piece % 36) * 16u);
   }
   long long slot_next = slot_of(0);
   for (int j = 0; j < w.tiles; ++j) {
@@ -255,10 +258,13 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
 #pragma unroll
     for (int i = 0; i < kRoundsCopy; ++i) {
-      const long long slot = __shfl_sync(0xffffffffu, slot_mine, src_row[i]);
+      const int piece = i * 32 + lane;
+      const int row = piece / 36, q = piece % 36;
+      const long long slot = __shfl_sync(0xffffffffu, slot_mine, row < kRowsPerWarp ? row : 0);
       // rows past the end are zero-filled (source size 0)
-      if (i * 32 + lane < kPiecesPerWarp)
-        cp_async16(tile + dst_off[i], kv + (slot < 0 ? 0 : slot) * kRowBytes + src_col[i], slot < 0 ? 0u : 16u);
+      if (piece < kPiecesPerWarp)
+        cp_async16(tile + dst_off[i], kv + (slot < 0 ? 0 : slot) * kRowBytes + static_cast<uint32_t>(q) * 16u,
+                   slot < 0 ? 0u : 16u);
     }
     cp_async_arrive(bars + 8 * (kMTileRaw + st));
     MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
@@ -777,7 +783,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
 template <int kPos, bool kTma>
 __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
   using C = Cfg<kPos>;
-  constexpr int kCopyThreads = copy_threads(kTma);
+  constexpr int kCopyThreads = copy_threads(kTma, kPos);
   constexpr int R = C::kRows, N = C::kN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -799,7 +805,7 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   constexpr int kMmaWarp = 4 * kPos, kFirstCopyWarp = kMmaWarp + 1;  // softmax warps, MMA warp, copy warps
   const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
   const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
-  constexpr int kPrepWarps = kFirstCopyWarp;
+  constexpr int kPrepWarps = kMmaWarp;  // the softmax warps
   const int prep_warp = warp;
   constexpr int kRounds = (R + kPrepWarps - 1) / kPrepWarps;  // 4: a warp takes rows prep_warp, + kPrepWarps, ...
   // A row is 72 pieces of 8 elements (16 bytes): a lane takes pieces lane, lane + 32 and (lanes 0-7) lane + 64.
@@ -809,7 +815,7 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   for (int k = 0; k < kRounds; ++k) {
     const int r = prep_warp + k * kPrepWarps;
     const int pos = w.pos0 + r / kHeadsMax, h = r % kHeadsMax;
-    const bool live = warp < kFirstCopyWarp && r < R && h < w.heads && pos < w.q_len;
+    const bool live = warp < kPrepWarps && r < R && h < w.heads && pos < w.q_len;
     const size_t qrow = (static_cast<size_t>(w.brow) * w.q_len + pos) * w.heads + h;
 #pragma unroll
     for (int i = 0; i < 3; ++i) {
@@ -841,17 +847,28 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
   MLA_TRACE_AT(5001, tid == 0);
-  // The query data is first looked at from here on (keeps the compiler from waiting for it above the barrier).
-#pragma unroll
-  for (int k = 0; k < kRounds; ++k)
-#pragma unroll
-    for (int i = 0; i < 3; ++i)
-      asm volatile("" : "+r"(vin[k][i].x), "+r"(vin[k][i].y), "+r"(vin[k][i].z), "+r"(vin[k][i].w));
-
-  // The copy warps start fetching at once; the other warps first turn the query rows into Q^T.
-  if (warp >= kFirstCopyWarp) {
+  // The copy warps start fetching at once; the softmax warps first turn the query rows into Q^T.
+  // Pools: the copy warps need few registers, the softmax warps many (setmaxnreg, each inside its own branch so
+  // that every role is compiled for its own budget).  The warpgroup that holds the MMA warp (descriptors kept in
+  // registers) and the first three copy warps keeps what it was launched with (128).
+  if (warp >= kMmaWarp + 4) {  // pools only: warpgroups of copy warps (and the padding warps behind them)
+    if constexpr (!kTma) {
+      setmaxnreg_dec<kPos == 1 ? 96 : 80>();
+      if (warp < kFirstCopyWarp + kCopyThreads / 32) role_copy<kPos, kTma>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
+    }
+  } else if (warp >= kFirstCopyWarp) {
     role_copy<kPos, kTma>(p, w, base, tid - kFirstCopyWarp * 32, ctx);
+  } else if (warp == kMmaWarp) {
+    asm volatile("bar.sync 1, %0;" ::"n"((kPrepWarps + 1) * 32) : "memory");  // Q^T is ready
+    if (lane == 0) role_mma<kPos, kTma>(w, smem, base, tmem, ctx);
   } else {
+    if constexpr (!kTma) setmaxnreg_inc<kPos == 1 ? 192 : 152>();
+    // The query data is first looked at from here on (keeps the compiler from waiting for it above the barrier).
+#pragma unroll
+    for (int k = 0; k < kRounds; ++k)
+#pragma unroll
+      for (int i = 0; i < 3; ++i)
+        asm volatile("" : "+r"(vin[k][i].x), "+r"(vin[k][i].y), "+r"(vin[k][i].z), "+r"(vin[k][i].w));
     // Query rows -> Q^T as two e4m3 terms per row.  Row r = position (r / 16) of the group, head (r % 16); a
     // row is scaled by the power of two that puts its largest magnitude into [128, 256), which makes
     // q * f = q1 + q2 exact for every element within 2^-7 of the largest (8 significant bits = 4 + 4).
@@ -904,13 +921,9 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
     }
     fence_proxy_async_smem();
     // every one of these warps gets here unconditionally: a plain named barrier is safe
-    asm volatile("bar.sync 1, %0;" ::"n"(kPrepWarps * 32) : "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"((kPrepWarps + 1) * 32) : "memory");
     MLA_TRACE_AT(5002, tid == 0);
-    if (warp < kMmaWarp) {
-      role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
-    } else if (warp == kMmaWarp) {
-      if (lane == 0) role_mma<kPos, kTma>(w, smem, base, tmem, ctx);
-    }
+    role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -1007,7 +1020,7 @@ extern "C" int ma_trace_read_mla(unsigned long long* host, int n) {
 #endif
 
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
-  if (p.pos_per_cta == 2 && p.use_tma) return launch_one<2, true>(p, stream);
+  if (p.pos_per_cta == 2) return p.use_tma ? launch_one<2, true>(p, stream) : launch_one<2, false>(p, stream);
   if (p.pos_per_cta != 1) return cudaErrorInvalidValue;
   return p.use_tma ? launch_one<1, true>(p, stream) : launch_one<1, false>(p, stream);
 }

@@ -49,14 +49,14 @@ def test_planner_fills_the_gpu_once_and_keeps_parts_long():
     plan = lambda B, q, S: _abi.lib.ma_mla_plan_parts(B, q, S, 148)
     assert plan(148, 1, 4096) == 1 and plan(300, 1, 4096) == 1
     assert plan(32, 1, 8192) == 4                # 148 // 32, 16 parts of four tiles available
-    assert plan(16, 4, 8192) == 2                # a window of four positions is four CTAs per part
+    assert plan(16, 4, 8192) == 4                # a window of four positions is two CTAs per part
     assert plan(1, 1, 131072) == 148             # one long request still fills the GPU
     assert plan(1, 1, 131072 * 4) == 148
     assert plan(1, 1, 1000) == 2                 # 8 tiles: at least four tiles per part
     assert plan(1, 1, 100) == 1
     assert plan(0, 1, 100) == 1 and plan(1, 9, 100) == 1
     slab = lambda B, q, S: _abi.lib.ma_mla_plan_parts_contiguous(B, q, S, 148)
-    assert slab(16, 4, 8192) == 4                # a contiguous cache: two positions per CTA, 32 CTAs before the split
+    assert slab(16, 4, 8192) == 4                # the contiguous launchers plan the same way
     assert slab(16, 5, 8192) == 3 and slab(148, 1, 4096) == 1 and slab(32, 1, 8192) == 4
     ws = _abi.lib.ma_mla_workspace_bytes
     assert ws(32, 1, 4) == 256 + 32 * 4 * 16 * 514 * 4
