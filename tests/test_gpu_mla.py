@@ -190,6 +190,20 @@ def test_e4m3_cache_is_read_unchanged(ma, cuda_device):
 
 
 @pytest.mark.parametrize("paged", [False, True])
+def test_e4m3_cache_in_a_window(ma, cuda_device, paged):
+    B, S, H, q_len = 2, 1100, 16, 5
+    kv = _rand_kv(B, S, cuda_device, 47, torch.float8_e4m3fn)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 47)
+    if paged:
+        pool, kv_indices, kv_indptr = _paged_pool(kv, [S] * B, cuda_device, 47)
+        lens = torch.tensor([S] * B, dtype=torch.int32, device=cuda_device)
+        ma.mla_decode_a16w8_multiq_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, 3, SCALE, KV_SCALE)
+    else:
+        ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, [S] * B, "fn"), f"e4m3fn cache, window of {q_len}, paged {paged}")
+
+
+@pytest.mark.parametrize("paged", [False, True])
 @pytest.mark.parametrize("density,exact", [(0.0005, True), (0.005, True), (0.05, False)])
 def test_saturated_fnuz_codes_are_corrected(ma, cuda_device, paged, density, exact):
     """0x7F / 0xFF are +-240 in e4m3-fnuz and NaN in the format the tensor core reads.  The kernel feeds +-224 and
