@@ -96,6 +96,24 @@ def test_lite_longest_first_matches_plain_bitexact(ma, cuda_device, monkeypatch)
     assert torch.equal(lpt, plain)
 
 
+def test_lite_several_tasks_per_cta_match_dense_forward(ma, cuda_device):
+    """384 tasks on 148 SMs: every CTA takes several tasks from the counter, task and verdict rings wrap.  With a
+    threshold nothing can reach, every call computes every block and must agree with the dense kernel."""
+    B, H, S = 2, 24, 2048
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(5)
+    q, k, v = (torch.randn(B, S, H, 128, generator=g, device=cuda_device).bfloat16() for _ in range(3))
+    ref = ma.forward(q, k, v, layout="bshd", round_mode="rtne").float()
+    attn = ma.LiteAttention(threshold=-1000.0, round_mode="rtne", layout="bshd")
+    for _ in range(3):  # both walk directions
+        out = attn(q, k, v)
+        torch.cuda.synchronize()
+        assert ma.last_status()[0] == 0
+        assert (out.float() - ref).abs().max().item() < 2e-3
+    rows = attn.read_list.cpu().numpy().reshape(-1, S // 64 + 2)
+    assert (rows[:, 0] == 2).all()  # one range, all 32 key blocks
+
+
 def test_lite_must_do_all_equals_compute_all(ma, cuda_device):
     s = LITE_SHAPE
     q, k, v = _peaked(cuda_device, "bshd", s["B"], s["S"], s["S"], s["H"])
