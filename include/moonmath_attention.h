@@ -201,12 +201,14 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
  *   kv_format: 0 = e4m3-fnuz, the reference's cache format; 1 = e4m3 (OCP).  The tensor core reads e4m3: fnuz
  *     bytes are reinterpreted (every finite value is exactly half).  0x7F / 0xFF (+-240), which are NaN in e4m3,
  *     are fed as +-224 and corrected by hand: exact for up to 640 such entries per 96 consecutive tokens of a
- *     request, +-224 for the surplus.  0x80 (NaN in fnuz) reads as zero.
+ *     request (256 when q_len > 1), +-224 for the surplus.  0x80 (NaN in fnuz) reads as zero.  An e4m3 cache is
+ *     read as it is; a NaN code in it reaches both draft positions of the CTA that reads the row (positions are
+ *     processed in pairs), also the one whose causal limit lies before that token.
  *   parts: KV split per request, 1..MA_MLA_MAX_PARTS (ma_mla_plan_parts); workspace: ma_mla_workspace_bytes.
  */
 #define MA_MLA_MAX_PARTS 256
 int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
-/* The same for a contiguous cache (kv_indices == NULL), where a CTA may take two draft positions of a window. */
+/* The split the contiguous entry points of the Python package choose for themselves (same rule). */
 int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms);
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts);
 int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
