@@ -287,6 +287,46 @@ def test_saturated_codes_under_zero_query_columns(ma, cuda_device):
     assert err < REL_L2, err
 
 
+def test_random_shapes_against_the_oracle(ma, cuda_device):
+    """Seeded sweep: ragged lengths down to fewer tokens than draft positions (positions without any token give
+    zeros), few heads, splits larger than the number of tiles, both cache formats, pool and contiguous."""
+    rng = np.random.default_rng(2024)
+    for case in range(24):
+        q_len = int(rng.choice([1, 2, 3, 4, 5, 7, 8]))
+        B, H = int(rng.integers(1, 5)), int(rng.choice([1, 3, 8, 16]))
+        fmt = "fnuz" if case % 3 else "fn"
+        dtype = torch.float8_e4m3fnuz if fmt == "fnuz" else torch.float8_e4m3fn
+        paged = bool(case % 2) or q_len in (2, 3)  # the contiguous window entry point takes 4..8 positions
+        lens = [int(x) for x in rng.choice([1, 2, 5, 95, 96, 97, 200, 777, 1500], size=B)]
+        if not paged:
+            lens = [max(lens)] * B
+        S = max(lens)
+        kv = _rand_kv(B, S, cuda_device, 100 + case, dtype)
+        q_lat, q_pe, o_lat = _rand_q(B, q_len if q_len > 1 else None, H, cuda_device, 100 + case)
+        o_lat.fill_(7.0)
+        if paged:
+            parts = int(rng.choice([1, 2, 5, 40]))
+            pool, kv_indices, kv_indptr = _paged_pool(kv, lens, cuda_device, 100 + case)
+            lens_t = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+            fn = ma.mla_decode_a16w8_paged_dev if q_len == 1 else ma.mla_decode_a16w8_multiq_paged_dev
+            if q_len in (2, 3):
+                fn = ma.mla_decode_a16w8_paged_dev
+            fn(q_lat, q_pe, pool, o_lat, lens_t, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+        elif q_len == 1:
+            ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+        else:
+            ma.mla_decode_a16w8_multiq(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+        torch.cuda.synchronize()
+        assert ma.last_status()[0] == 0, (case, ma.last_status())
+        want = _oracle(q_lat, q_pe, kv, lens, fmt)
+        got = o_lat.float().cpu().numpy().reshape(want.shape)
+        assert np.isfinite(got).all(), case
+        empty = np.abs(want).reshape(want.shape[0], want.shape[1], -1).max(axis=-1) == 0  # positions without tokens
+        assert (got[empty] == 0).all(), case
+        err = mo.rel_l2(got, want)
+        assert err < REL_L2, (case, q_len, B, H, lens, fmt, paged, err)
+
+
 def test_contiguous_argument_errors(ma, cuda_device):
     kv = _rand_kv(2, 256, cuda_device, 83)
     q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
