@@ -327,6 +327,46 @@ def test_random_shapes_against_the_oracle(ma, cuda_device):
         assert err < REL_L2, (case, q_len, B, H, lens, fmt, paged, err)
 
 
+def test_paged_call_replays_from_a_cuda_graph(ma, cuda_device):
+    """All index arrays are read on the device and the grid depends on (batch, q_len, parts) only: a captured call
+    replays correctly after the lengths, the slot table and the queries have changed in place."""
+    B, H, q_len, parts, S = 3, 16, 4, 3, 1500
+    kv = _rand_kv(B, S, cuda_device, 61)
+    q_lat, q_pe, o_lat = _rand_q(B, q_len, H, cuda_device, 61)
+    lens0, lens1 = [S, 900, 1200], [700, S, 333]
+    pool, idx0, indptr0 = _paged_pool(kv, lens0, cuda_device, 61)
+    _, idx1, indptr1 = _paged_pool(kv, lens1, cuda_device, 62)
+    kv_indices = torch.zeros(B * S, dtype=torch.int32, device=cuda_device)
+    kv_indptr = torch.zeros(B + 1, dtype=torch.int32, device=cuda_device)
+    lens_t = torch.zeros(B, dtype=torch.int32, device=cuda_device)
+    # one pool that holds both layouts: the second permutation's rows go behind the first's
+    pool1, _, _ = _paged_pool(kv, lens1, cuda_device, 62)
+    both = torch.cat([pool, pool1], dim=0)
+
+    def load(lens, idx, indptr, offset):
+        lens_t.copy_(torch.tensor(lens, dtype=torch.int32))
+        kv_indices[: idx.numel()] = idx + offset
+        kv_indptr.copy_(indptr)
+
+    load(lens0, idx0, indptr0, 0)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):  # warm-up outside the capture, as torch asks
+        ma.mla_decode_a16w8_multiq_paged_dev(q_lat, q_pe, both, o_lat, lens_t, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ma.mla_decode_a16w8_multiq_paged_dev(q_lat, q_pe, both, o_lat, lens_t, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    graph.replay()
+    torch.cuda.synchronize()
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, lens0), "graph replay, first lengths")
+    load(lens1, idx1, indptr1, pool.shape[0])
+    q_lat.copy_(_rand_q(B, q_len, H, cuda_device, 63)[0])
+    graph.replay()
+    torch.cuda.synchronize()
+    _check(ma, o_lat, _oracle(q_lat, q_pe, kv, lens1), "graph replay, second lengths")
+
+
 def test_contiguous_argument_errors(ma, cuda_device):
     kv = _rand_kv(2, 256, cuda_device, 83)
     q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
