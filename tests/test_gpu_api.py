@@ -93,6 +93,41 @@ def test_concurrent_calls_on_two_streams_do_not_interfere(ma, cuda_device):
         assert torch.equal(got_b.view(torch.int16), want_b.view(torch.int16))
 
 
+def test_forward_and_lite_replay_from_a_cuda_graph(ma, cuda_device, monkeypatch):
+    """The dense call (memset, main kernel and, where the plan splits the last wave, merge; 240 tasks here) and a
+    LiteAttention call keep no host state between launches: captured once, they replay bit-identically on new data."""
+    monkeypatch.delenv("MOONMATH_CHECK", raising=False)  # the check synchronises after every call
+    g = torch.Generator(device=cuda_device)
+    g.manual_seed(9)
+    q, k, v = (torch.randn(1, 1300, 40, 128, generator=g, device=cuda_device).bfloat16() for _ in range(3))
+    out = torch.empty_like(q)
+    lists = torch.zeros(2, 1, 40, 6, 23, dtype=torch.int16, device=cuda_device)  # ceil(1300/256) x (ceil(1300/64) + 2)
+    lists[0, ..., 0], lists[0, ..., 1], lists[0, ..., 2] = 2, 20, -1
+    out_lite = torch.empty_like(q)
+
+    def calls():
+        ma.forward(q, k, v, out=out, layout="bshd", round_mode="rtna")
+        ma.forward_lite(q, k, v, lists[0], lists[1], threshold=-1000.0, phase=1, out=out_lite, layout="bshd", round_mode="rtna")
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        calls()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        calls()
+    q.copy_(torch.randn(q.shape, generator=g, device=cuda_device).bfloat16())
+    graph.replay()
+    torch.cuda.synchronize()
+    got, got_lite = out.clone(), out_lite.clone()
+    calls()
+    torch.cuda.synchronize()
+    assert ma.last_status()[0] == 0
+    assert torch.equal(got.view(torch.int16), out.view(torch.int16))
+    assert torch.equal(got_lite.view(torch.int16), out_lite.view(torch.int16))
+
+
 def test_randomised_shapes_against_the_oracle(ma):
     """Seeded sweep over batch, heads, ragged lengths, layouts and modes (small enough for the CPU oracle)."""
     rng = np.random.default_rng(2026)
