@@ -6,7 +6,7 @@ queries, outputs and split partials are a few hundred KB).  Reported: median mic
 passes of `--iters` calls between two CUDA events, and that traffic divided by the time, next to the measured copy
 bandwidth of the GPU when MEASURED_PEAKS.json is found beside the repository root.
 
-    python amd-kernels_b200/bench_mla.py [--paged [--sequential]] [--format fnuz|fn] [--json out.json]
+    python amd-kernels_b200/bench_mla.py [--paged [--sequential]] [--format fnuz|fn] [--graph] [--json out.json]
 """
 from __future__ import annotations
 
@@ -35,6 +35,7 @@ def main() -> None:
     ap.add_argument("--format", default="fnuz", choices=("fnuz", "fn"))
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--passes", type=int, default=5)
+    ap.add_argument("--graph", action="store_true", help="capture the call in a CUDA graph and time replays")
     ap.add_argument("--json", default="")
     args = ap.parse_args()
 
@@ -75,6 +76,11 @@ def main() -> None:
             call()
         torch.cuda.synchronize()
         assert ma.last_status()[0] == 0
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                call()
+            call = graph.replay
         us = []
         for _ in range(args.passes):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -88,7 +94,7 @@ def main() -> None:
         gbs = B * S * FUSED / t / 1e3
         frac = f"  {100.0 * gbs / peak:5.1f} % of measured copy bandwidth" if peak else ""
         print(f"B={B:4d} S={S:7d} q_len={q_len} {'paged' if args.paged else 'slab '} {args.format}: {t:8.1f} us  {gbs:7.0f} GB/s{frac}")
-        results.append({"batch": B, "seq_len": S, "q_len": q_len, "paged": args.paged, "format": args.format, "us": t, "gbs": gbs})
+        results.append({"batch": B, "seq_len": S, "q_len": q_len, "paged": args.paged, "format": args.format, "graph": args.graph, "us": t, "gbs": gbs})
         del kv
     if args.json:
         with open(args.json, "w") as f:
