@@ -57,6 +57,19 @@ constexpr uint32_t kOffTmemSlot = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
 constexpr size_t kSmemBytes = kOffAbort + 4 + 1024;  // + alignment slack
 
+#ifdef MA_TRACE
+// Development-only timestamp trace (built into a separate library, never into the product build).
+__device__ unsigned long long g_trace_lite[8192];
+#define LITE_TRACE_AT(slot, cond)                                                       \
+  do {                                                                                  \
+    if ((cond) && blockIdx.x == 0 && (slot) < 8192) g_trace_lite[(slot)] = clock64(); \
+  } while (0)
+#else
+#define LITE_TRACE_AT(slot, cond) \
+  do {                            \
+  } while (0)
+#endif
+
 #define MA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), (site), ctx)) return
 #define MA_WAIT_WARP(bar, parity, site) \
@@ -118,10 +131,12 @@ __device__ __forceinline__ void role_producer(const LiteParams& p, uint8_t* smem
     tasks[(it % kTaskRing) * 2 + 1] = kept;
     mbar_arrive(bars + 8 * (kBarTask + (it % kTaskRing)));
     if (id < 0) return;
+    LITE_TRACE_AT(it * 16 + 0, it < 500);
     const int16_t* row = p.read_list + static_cast<size_t>(id) * p.row_width;
     const Task t = decode_task(p, id, kept);
     const int q_row0 = t.qb * kTaskRows;
     if (it > 0) MA_WAIT_SLEEP(kSleepProducer, bars + 8 * kBarQEmpty, (it - 1) & 1, 0x10);
+    LITE_TRACE_AT(it * 16 + 1, it < 500);
     mbar_arrive_expect_tx(bars + 8 * (kBarQFull + 0), kTileBytes);
     tma_load_tile<kTileM>(base + kOffQ, &p.a.tm_q, bars + 8 * (kBarQFull + 0), p.a.bshd, q_row0, t.h, t.b);
     ListCursor cur;
@@ -162,8 +177,13 @@ __device__ __forceinline__ void role_producer(const LiteParams& p, uint8_t* smem
                                 q_row0 + kTileM, t.h, t.b);
         }
       }
-      if (j == 0) fetch(id, kept);
+      if (j == 0) {
+        LITE_TRACE_AT(it * 16 + 2, it < 500);
+        fetch(id, kept);
+        LITE_TRACE_AT(it * 16 + 3, it < 500);
+      }
     }
+    LITE_TRACE_AT(it * 16 + 4, it < 500);
   }
 }
 
@@ -182,6 +202,7 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
   for (uint32_t it = 0;; ++it) {
     MA_NEXT_TASK(MA_WAIT, t, 0x2F);
     const int n = t.steps;
+    LITE_TRACE_AT(it * 16 + 5, it < 500);
     {
       const uint32_t st = fill % kStages;
       MA_WAIT(bars + 8 * (kBarKvFull + st), (fill / kStages) & 1, 0x21);
@@ -195,6 +216,7 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
       }
       umma_commit(bars + 8 * (kBarKvEmpty + st));
       if (n == 1) umma_commit(bars + 8 * kBarQEmpty);
+      LITE_TRACE_AT(it * 16 + 6, it < 500);
     }
     for (int j = 0; j < n; ++j, ++blk) {
       const uint32_t fv = fill + 2 * j + 1, sv = fv % kStages;  // V(j)
@@ -224,6 +246,7 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
       }
     }
     fill += 2 * static_cast<uint32_t>(n);
+    LITE_TRACE_AT(it * 16 + 7, it < 500);
   }
 }
 
@@ -293,6 +316,7 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
   for (uint32_t it = 0;; ++it) {
     MA_NEXT_TASK(MA_WAIT_WARP, t, 0x3F);
     const int n = t.steps;
+    LITE_TRACE_AT(it * 16 + 8 + tile * 3, row == 0 && it < 500);
     const bool live = t.qb * kTaskRows + tile * kTileM + row < p.a.seq_q;
     ListCursor cur;
     cur.init(p.read_list + static_cast<size_t>(t.id) * p.row_width, p.phase);
@@ -311,6 +335,7 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       if (sb.b1 >= 0) sb.e1 = cur.advance();
 
       MA_WAIT_WARP_SLEEP(kSleepSoftmax, bar_s, blk & 1, 0x30 + tile);
+      LITE_TRACE_AT(it * 16 + 9 + tile * 3, row == 0 && it < 500 && j == 0);
       tc_fence_after_sync();
       // S(j) of tile 0 follows P V (j-1) of tile 0 in the MMA order, which follows P V (j-2) of tile 1:
       // every warp's votes of step j - 2 are in shared memory.
@@ -387,6 +412,7 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       hist2 = hist1;
       hist1 = sb;
     }
+    LITE_TRACE_AT(it * 16 + 10 + tile * 3, row == 0 && it < 500);
     if (emits && t.kept > 0) {
       // The last two steps: wait until every softmax thread of both tiles has finished them.
       MA_WAIT(bars + 8 * (kBarPFull + 0), (blk - 1) & 1, 0x38);
@@ -440,6 +466,7 @@ __device__ __forceinline__ void role_epilogue(const LiteParams& p, uint8_t* smem
       }
       tc_fence_before_sync();
       mbar_arrive(bars + 8 * (kBarOFree + tile));
+      LITE_TRACE_AT(it * 16 + 14 + tile, row == 0 && it < 500);
     }
   }
 }
@@ -534,6 +561,12 @@ cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stre
                                            p.phase);
   return cudaGetLastError();
 }
+
+#ifdef MA_TRACE
+extern "C" int ma_trace_read_lite(unsigned long long* host, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_lite, sizeof(unsigned long long) * n));
+}
+#endif
 
 cudaError_t launch_attn_lite(const LiteParams& p, int grid, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(attn_lite_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
