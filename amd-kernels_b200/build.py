@@ -24,7 +24,7 @@ PKG = HERE / "moonmath_attention"
 LIB = PKG / "libmoonmath_attention_sm100.so"
 OBJ_DIR = HERE / "build"
 
-SOURCES = ["ma_abi.cu", "attn_simple.cu", "attn_pipelined.cu", "attn_lite.cu", "attn_merge.cu", "mla_decode.cu"]
+SOURCES = ["ma_abi.cu", "attn_simple.cu", "attn_pipelined.cu", "attn_lite.cu", "attn_merge.cu", "mla_decode.cu", "selftest.cu"]
 HEADERS = ["sm100_ptx.cuh", "attn_common.cuh", "attn_launch.h", "tail_plan.h", "lite_list.h"]
 
 # `-arch=sm_100a` also emits a plain compute_100 PTX pass that rejects tcgen05;

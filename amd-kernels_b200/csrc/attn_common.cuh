@@ -26,9 +26,9 @@ enum RoundMode : int { kRTNE = 0, kRTNA = 1, kRTZ = 2 };
 constexpr int kStatusWords = 64;
 constexpr uint32_t kErrWaitTimeout = 0x57A17u;
 
-// Wall-clock bound of one mbarrier wait.  A healthy wait lasts microseconds; the
+// Default wall-clock bound of one mbarrier wait.  A healthy wait lasts microseconds; the
 // longest legitimate one (an epilogue warp waiting for a whole long task) stays
-// far below this.
+// far below this.  A kernel may run its waits under another bound (WaitCtx::limit_ns).
 constexpr uint64_t kWaitLimitNs = 2000ull * 1000ull * 1000ull;
 
 struct AttnParams {
@@ -93,6 +93,7 @@ struct MlaParams {
 struct WaitCtx {
   uint32_t* status;     // global status block or null
   volatile int* abort;  // shared-memory flag: some thread of this CTA gave up
+  uint64_t limit_ns = kWaitLimitNs;  // how long one wait may last before it is abandoned
 };
 
 __device__ __forceinline__ void record_error(uint32_t* status, uint32_t code, uint32_t site, uint32_t detail) {
@@ -134,7 +135,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, ui
       const uint64_t now = sm100::globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > ctx.limit_ns) {
         record_error(ctx.status, kErrWaitTimeout, site, parity);
         *ctx.abort = 1;
         return false;
@@ -219,29 +220,6 @@ __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
   return d;
 }
 
-// 2^x for a pair on the FMA pipe instead of the special-function unit: x is clamped to >= -126,
-// split as n + f with n = round(x), f in [-1/2, 1/2]; 2^f by a degree-3 minimax polynomial
-// (maximum relative error 7.5e-5, far below the 2^-9 of the bf16 rounding applied to P afterwards);
-// n goes straight into the exponent field.  Valid for finite x <= 127 and x = -inf (gives ~2^-126);
-// NaN must not reach it: callers route rows with a non-finite maximum to ex2_approx.
-__device__ __forceinline__ void ex2_poly2(f32x2 x, float& p0, float& p1) {
-  constexpr float kMagic = 12582912.f;  // 1.5 * 2^23: adding it leaves round(x) in the low mantissa bits
-  float x0, x1;
-  unpack2(x, x0, x1);
-  const f32x2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
-  const f32x2 xr = add2(xc, pack2(kMagic, kMagic));
-  const f32x2 nf = add2(xr, pack2(-kMagic, -kMagic));
-  const f32x2 f = fma2(nf, pack2(-1.f, -1.f), xc);
-  f32x2 p = fma2(f, pack2(0.05517132207751274f, 0.05517132207751274f), pack2(0.24261054396629333f, 0.24261054396629333f));
-  p = fma2(p, f, pack2(0.6932609677314758f, 0.6932609677314758f));
-  p = fma2(p, f, pack2(0.9999281167984009f, 0.9999281167984009f));
-  float r0, r1, q0, q1;
-  unpack2(xr, r0, r1);
-  unpack2(p, q0, q1);
-  p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-  p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
-}
-
 // Packs two probabilities as bf16 for the P operand of the second MMA (`lo` has the lower key index).
 // The tensor core takes A and B of one 16-bit format only: a kind::f16 MMA with fp16 A and bf16 B is
 // an illegal instruction on sm_100, so P shares V's bf16.  P is rounded to nearest-even in every
@@ -249,6 +227,12 @@ __device__ __forceinline__ void ex2_poly2(f32x2 x, float& p0, float& p1) {
 __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
   const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// What rounding (lo, hi) to the bf16 pair `packed` left over, again as a bf16 pair: the residual of a
+// round-to-nearest is exactly representable in fp32, so P_hi + P_lo carries p to 16 significant bits.
+__device__ __forceinline__ uint32_t pack_p_residual(float lo, float hi, uint32_t packed) {
+  return pack_p(lo - __uint_as_float(packed << 16), hi - __uint_as_float(packed & 0xFFFF0000u));
 }
 
 // Address (in elements) of output row `row` of slice (b, h).

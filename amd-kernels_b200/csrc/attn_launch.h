@@ -18,8 +18,8 @@ struct MlaParams;
 cudaError_t launch_attn_simple(const AttnParams& p, cudaStream_t stream);
 
 // Persistent warp-specialised kernel; `grid` CTAs walk the unit list of the plan.
-// `poly_of_4`: of every four score pairs, how many take the polynomial 2^x (rest: special-function unit).
-cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, int poly_of_4, cudaStream_t stream);
+// `precise_p`: feed the probabilities to the second MMA as a sum of two bf16 terms (MA_FLAG_PRECISE_P).
+cudaError_t launch_attn_pipelined(const AttnParams& p, int grid, bool precise_p, cudaStream_t stream);
 
 // Combines the partial results of KV-split tasks into the bf16 output.
 cudaError_t launch_merge_parts(const AttnParams& p, cudaStream_t stream);
@@ -31,6 +31,10 @@ cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stre
 
 // MLA absorbed decode: one CTA per (request, group of draft positions, KV part), then the merge of the parts.
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream);
+
+// One CTA that waits, under `limit_ns`, on a barrier nobody arrives on: exercises the time-out branch of the
+// bounded waits, the status words and the unwind that frees tensor memory.  `status`: 64 zeroed words.
+cudaError_t launch_wait_timeout_selftest(uint32_t* status, uint64_t limit_ns, cudaStream_t stream);
 
 // dst[i] = bf16(src[i]) with the given rounding mode (device pointers); exposes the
 // epilogue's rounding code for exhaustive bit-pattern tests.

@@ -31,7 +31,10 @@ constexpr int kStages = 4;  // K/V ring, 32 KiB each
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kSleepProducer = 128, kSleepSoftmax = 32, kSleepEpilogue = 1000;
 constexpr int kTaskRing = 4;     // task descriptors in flight: producer, MMA, softmax and epilogue span < 4 tasks
-constexpr int kVerdictRing = 4;  // steps whose votes are kept: the emitter runs two steps behind
+// Steps whose votes are kept.  Slots are indexed by the CTA-wide step counter, not the step within a task: the
+// emitter reads steps c - 2 and c - 1 while the warps it does not gate may already vote on step c of the
+// next task (never c + 1: that needs the emitter's own arrival on p_full), so four slots never collide.
+constexpr int kVerdictRing = 4;
 
 // shared-memory map (offsets from a 1024-byte aligned base)
 constexpr uint32_t kOffQ = 0;                                    // 2 tiles
@@ -51,24 +54,13 @@ enum Bar : uint32_t {
   kBarOFree = kBarOFull + 2,           // [2]       epilogue -> MMA (128 arrivals)
   kBarLReady = kBarOFree + 2,          // [2]       softmax -> epilogue (128 arrivals)
   kBarTask = kBarLReady + 2,           // [kTaskRing] producer -> everyone: task descriptor written
-  kNumBars = kBarTask + kTaskRing
+  kBarVotes = kBarTask + kTaskRing,    //           softmax -> list emitter: a task's votes are all in (256 arrivals)
+  kNumBars = kBarVotes + 1
 };
 constexpr uint32_t kOffTmemSlot = kOffBars + kNumBars * 8;
 constexpr uint32_t kOffAbort = kOffTmemSlot + 4;
 constexpr size_t kSmemBytes = kOffAbort + 4 + 1024;  // + alignment slack
 
-#ifdef MA_TRACE
-// Development-only timestamp trace (built into a separate library, never into the product build).
-__device__ unsigned long long g_trace_lite[8192];
-#define LITE_TRACE_AT(slot, cond)                                                       \
-  do {                                                                                  \
-    if ((cond) && blockIdx.x == 0 && (slot) < 8192) g_trace_lite[(slot)] = clock64(); \
-  } while (0)
-#else
-#define LITE_TRACE_AT(slot, cond) \
-  do {                            \
-  } while (0)
-#endif
 
 #define MA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), (site), ctx)) return
@@ -131,12 +123,10 @@ __device__ __forceinline__ void role_producer(const LiteParams& p, uint8_t* smem
     tasks[(it % kTaskRing) * 2 + 1] = kept;
     mbar_arrive(bars + 8 * (kBarTask + (it % kTaskRing)));
     if (id < 0) return;
-    LITE_TRACE_AT(it * 16 + 0, it < 500);
     const int16_t* row = p.read_list + static_cast<size_t>(id) * p.row_width;
     const Task t = decode_task(p, id, kept);
     const int q_row0 = t.qb * kTaskRows;
     if (it > 0) MA_WAIT_SLEEP(kSleepProducer, bars + 8 * kBarQEmpty, (it - 1) & 1, 0x10);
-    LITE_TRACE_AT(it * 16 + 1, it < 500);
     mbar_arrive_expect_tx(bars + 8 * (kBarQFull + 0), kTileBytes);
     tma_load_tile<kTileM>(base + kOffQ, &p.a.tm_q, bars + 8 * (kBarQFull + 0), p.a.bshd, q_row0, t.h, t.b);
     ListCursor cur;
@@ -178,12 +168,9 @@ __device__ __forceinline__ void role_producer(const LiteParams& p, uint8_t* smem
         }
       }
       if (j == 0) {
-        LITE_TRACE_AT(it * 16 + 2, it < 500);
         fetch(id, kept);
-        LITE_TRACE_AT(it * 16 + 3, it < 500);
       }
     }
-    LITE_TRACE_AT(it * 16 + 4, it < 500);
   }
 }
 
@@ -202,7 +189,6 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
   for (uint32_t it = 0;; ++it) {
     MA_NEXT_TASK(MA_WAIT, t, 0x2F);
     const int n = t.steps;
-    LITE_TRACE_AT(it * 16 + 5, it < 500);
     {
       const uint32_t st = fill % kStages;
       MA_WAIT(bars + 8 * (kBarKvFull + st), (fill / kStages) & 1, 0x21);
@@ -216,7 +202,6 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
       }
       umma_commit(bars + 8 * (kBarKvEmpty + st));
       if (n == 1) umma_commit(bars + 8 * kBarQEmpty);
-      LITE_TRACE_AT(it * 16 + 6, it < 500);
     }
     for (int j = 0; j < n; ++j, ++blk) {
       const uint32_t fv = fill + 2 * j + 1, sv = fv % kStages;  // V(j)
@@ -246,7 +231,6 @@ __device__ __forceinline__ void role_mma(const LiteParams& p, uint8_t* smem, uin
       }
     }
     fill += 2 * static_cast<uint32_t>(n);
-    LITE_TRACE_AT(it * 16 + 7, it < 500);
   }
 }
 
@@ -316,7 +300,6 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
   for (uint32_t it = 0;; ++it) {
     MA_NEXT_TASK(MA_WAIT_WARP, t, 0x3F);
     const int n = t.steps;
-    LITE_TRACE_AT(it * 16 + 8 + tile * 3, row == 0 && it < 500);
     const bool live = t.qb * kTaskRows + tile * kTileM + row < p.a.seq_q;
     ListCursor cur;
     cur.init(p.read_list + static_cast<size_t>(t.id) * p.row_width, p.phase);
@@ -335,11 +318,10 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       if (sb.b1 >= 0) sb.e1 = cur.advance();
 
       MA_WAIT_WARP_SLEEP(kSleepSoftmax, bar_s, blk & 1, 0x30 + tile);
-      LITE_TRACE_AT(it * 16 + 9 + tile * 3, row == 0 && it < 500 && j == 0);
       tc_fence_after_sync();
       // S(j) of tile 0 follows P V (j-1) of tile 0 in the MMA order, which follows P V (j-2) of tile 1:
       // every warp's votes of step j - 2 are in shared memory.
-      if (emits && j >= 2) rec.step(hist2, verdict + ((j - 2) % kVerdictRing) * 8, false);
+      if (emits && j >= 2) rec.step(hist2, verdict + ((blk - 2) % kVerdictRing) * 8, false);
 
       uint32_t s[128];
       tmem_ld128_sync(tS, s);
@@ -363,7 +345,7 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       const bool want1 = live && sb.b1 >= 0 && (m1 - ref1) > thr;
       const bool keep0 = first || __any_sync(0xffffffffu, want0);
       const bool keep1 = __any_sync(0xffffffffu, want1);
-      if (lane0) verdict[(j % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
+      if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
       if (!keep0 || !keep1) {
         // A skipping warp contributes nothing for the block and its state does not see it.
 #pragma unroll
@@ -412,13 +394,13 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       hist2 = hist1;
       hist1 = sb;
     }
-    LITE_TRACE_AT(it * 16 + 10 + tile * 3, row == 0 && it < 500);
+    // One phase of the votes barrier per task: it completes when all 256 softmax threads have cast their
+    // last vote of this task, and cannot run ahead (the next phase needs the emitter's own arrival).
+    mbar_arrive(bars + 8 * kBarVotes);
     if (emits && t.kept > 0) {
-      // The last two steps: wait until every softmax thread of both tiles has finished them.
-      MA_WAIT(bars + 8 * (kBarPFull + 0), (blk - 1) & 1, 0x38);
-      MA_WAIT(bars + 8 * (kBarPFull + 1), (blk - 1) & 1, 0x39);
-      if (n >= 2) rec.step(hist2, verdict + ((n - 2) % kVerdictRing) * 8, false);
-      rec.step(hist1, verdict + ((n - 1) % kVerdictRing) * 8, true);
+      MA_WAIT(bars + 8 * kBarVotes, it & 1, 0x38);
+      if (n >= 2) rec.step(hist2, verdict + ((blk - 2) % kVerdictRing) * 8, false);
+      rec.step(hist1, verdict + ((blk - 1) % kVerdictRing) * 8, true);
       rec.out.finish();
     }
     // The epilogue must have consumed the previous task's l_ready phase before this one completes.
@@ -466,7 +448,6 @@ __device__ __forceinline__ void role_epilogue(const LiteParams& p, uint8_t* smem
       }
       tc_fence_before_sync();
       mbar_arrive(bars + 8 * (kBarOFree + tile));
-      LITE_TRACE_AT(it * 16 + 14 + tile, row == 0 && it < 500);
     }
   }
 }
@@ -485,7 +466,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_lite_kernel(const __grid_con
     for (uint32_t i = 0; i < kNumBars; ++i) {
       const bool many = (i >= kBarPFull && i < kBarPFull + 2) || (i >= kBarOFree && i < kBarOFree + 2) ||
                         (i >= kBarLReady && i < kBarLReady + 2);
-      mbar_init(bars + 8 * i, many ? 128u : 1u);
+      mbar_init(bars + 8 * i, i == kBarVotes ? 256u : (many ? 128u : 1u));
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -562,11 +543,6 @@ cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stre
   return cudaGetLastError();
 }
 
-#ifdef MA_TRACE
-extern "C" int ma_trace_read_lite(unsigned long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_lite, sizeof(unsigned long long) * n));
-}
-#endif
 
 cudaError_t launch_attn_lite(const LiteParams& p, int grid, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(attn_lite_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

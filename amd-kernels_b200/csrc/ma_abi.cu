@@ -1,8 +1,9 @@
 // C ABI of the library (declared in include/moonmath_attention.h): argument
 // checks, tensor maps, tail plan, kernel launches.  Keeps no state between
-// calls apart from the lazily resolved driver entry point.
+// calls apart from the lazily resolved driver entry point and, for
+// ma_attention_forward_static only, the static scratch array and its cached
+// per-device address.
 #include <cmath>
-#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -73,6 +74,10 @@ int make_kv_slab_map(CUtensorMap* tm, const void* ptr, int batch, int seq, int w
 
 int cuda_rc(cudaError_t e) { return e == cudaSuccess ? MA_OK : MA_ERR_CUDA_BASE + static_cast<int>(e); }
 
+// Flag bits each entry point understands; anything else is refused rather than ignored.
+constexpr int kForwardFlags = MA_FLAG_NO_TAIL | MA_FLAG_SIMPLE | MA_FLAG_EXACT_MAX | MA_FLAG_PRECISE_P;
+constexpr int kLiteFlags = MA_FLAG_LITE_PLAIN;
+
 int check_dims(int batch, int heads, int seq_len, int seq_len_kv) {
   if (batch <= 0 || heads <= 0) return MA_ERR_BATCH_HEADS;
   if (seq_len <= 0) return MA_ERR_SEQ_Q;
@@ -110,6 +115,14 @@ int static_scratch_address(int dev, void** out) {
   return MA_OK;
 }
 
+// Forgets the cached address of a device, so that the next call asks the runtime again.  Called when a
+// launch through the cached address failed: after cudaDeviceReset the old address is stale.
+void forget_static_scratch_address(int dev) {
+  if (dev < 0 || dev >= kMaxDevices) return;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  g_static_addr[dev] = nullptr;
+}
+
 int resolve_sms(int num_sms) {
   if (num_sms > 0) return num_sms;
   return ma_device_sms();
@@ -141,6 +154,7 @@ const char* ma_error_string(int rc) {
     case MA_ERR_TOO_LARGE: return "problem exceeds the kernel's index range";
     case MA_ERR_LITE_ARGS: return "threshold must be negative, phase 0 or 1, at most 32766 key blocks of 64";
     case MA_ERR_MLA_ARGS: return "parts must be in [1, MA_MLA_MAX_PARTS], kv_format 0 (e4m3-fnuz) or 1 (e4m3)";
+    case MA_ERR_FLAGS: return "flags holds a bit this entry point does not define";
     case MA_ERR_STATIC_SCRATCH:
       return "problem needs more scratch than the built-in static buffer holds (pass MA_FLAG_NO_TAIL or use "
              "ma_attention_forward with a workspace)";
@@ -185,6 +199,7 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
   if (head_dim != ma::kHeadDim) return MA_ERR_HEAD_DIM;
   if (layout != MA_LAYOUT_BHSD && layout != MA_LAYOUT_BSHD) return MA_ERR_LAYOUT;
   if (round_mode < MA_ROUND_RTNE || round_mode > MA_ROUND_RTZ) return MA_ERR_ROUND_MODE;
+  if (flags & ~kForwardFlags) return MA_ERR_FLAGS;
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return MA_ERR_NULL_POINTER;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
@@ -236,8 +251,7 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
     if (e != cudaSuccess) return cuda_rc(e);
   }
   if (simple) return cuda_rc(ma::launch_attn_simple(p, stream));
-  const int poly = (flags & 0x800) ? ((flags >> 8) & 7) : 0;  // bits 8-11: tuning override
-  e = ma::launch_attn_pipelined(p, plan.grid, poly, stream);
+  e = ma::launch_attn_pipelined(p, plan.grid, (flags & MA_FLAG_PRECISE_P) != 0, stream);
   if (e == cudaSuccess && plan.tail_tasks > 0) e = ma::launch_merge_parts(p, stream);
   return cuda_rc(e);
 }
@@ -245,8 +259,9 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
 int ma_attention_forward_static(const void* q, const void* k, const void* v, void* out, int batch, int heads,
                                 int seq_len, int seq_len_kv, int head_dim, int layout, int round_mode, int flags,
                                 void* stream) {
-  const int rc = check_dims(batch, heads, seq_len, seq_len_kv);
+  int rc = check_dims(batch, heads, seq_len, seq_len_kv);
   if (rc != MA_OK) return rc;
+  if (flags & ~kForwardFlags) return MA_ERR_FLAGS;
   int dev = 0, sms = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -260,8 +275,12 @@ int ma_attention_forward_static(const void* q, const void* k, const void* v, voi
   if (arc != MA_OK) return arc;
   // Same kernels and plan as ma_attention_forward, with the static buffer as its workspace.  That
   // call clears the status block; the partial results are fully rewritten before the merge reads them.
-  return ma_attention_forward(q, k, v, out, batch, heads, seq_len, seq_len_kv, head_dim, layout, round_mode, scratch,
-                              kStaticScratchBytes, flags, stream);
+  rc = ma_attention_forward(q, k, v, out, batch, heads, seq_len, seq_len_kv, head_dim, layout, round_mode, scratch,
+                            kStaticScratchBytes, flags, stream);
+  // A CUDA error on the way may mean that the cached address went stale (cudaDeviceReset since the
+  // look-up): drop it, so that the next call asks the runtime again.
+  if (rc >= MA_ERR_CUDA_BASE) forget_static_scratch_address(dev);
+  return rc;
 }
 
 int ma_static_status(uint32_t* host_words, int n, void* stream_) {
@@ -300,6 +319,7 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
   if (read_list == nullptr || write_list == nullptr) return MA_ERR_LISTS;
   if (layout != MA_LAYOUT_BHSD && layout != MA_LAYOUT_BSHD) return MA_ERR_LAYOUT;
   if (round_mode < MA_ROUND_RTNE || round_mode > MA_ROUND_RTZ) return MA_ERR_ROUND_MODE;
+  if (flags & ~kLiteFlags) return MA_ERR_FLAGS;
   if (q == nullptr || k == nullptr || v == nullptr || out == nullptr) return MA_ERR_NULL_POINTER;
   const uintptr_t bits = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                          reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(out);
@@ -358,20 +378,17 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
 // ---- MLA absorbed decode -------------------------------------------------------------------------------
 namespace {
 // Draft positions per CTA: two for a window (a second group of softmax warps on the same tiles), the way the
-// reference's multi-query kernel keeps a window resident (csrc/mla_decode_a16w8_multiq.hip:722).  MA_MLA_POS1=1 is a
-// development switch back to one CTA per position.
-int mla_pos_per_cta(int q_len, bool) { return q_len >= 2 && std::getenv("MA_MLA_POS1") == nullptr ? 2 : 1; }
-// Development switch: MA_MLA_NO_TMA=1 sends a contiguous slab through the copy path of the paged pool.
-bool flags_env_no_tma() { return std::getenv("MA_MLA_NO_TMA") != nullptr; }
+// reference's multi-query kernel keeps a window resident (csrc/mla_decode_a16w8_multiq.hip:722).
+int mla_pos_per_cta(int q_len) { return q_len >= 2 ? 2 : 1; }
 int mla_groups(int q_len, int per) { return (q_len + per - 1) / per; }
 }  // namespace
 
 namespace {
-int mla_plan(int batch, int q_len, int max_seq_len, int num_sms, bool slab) {
+int mla_plan(int batch, int q_len, int max_seq_len, int num_sms) {
   if (batch <= 0 || q_len < 1 || q_len > 8 || max_seq_len <= 0) return 1;
   const int sms = resolve_sms(num_sms);
   if (sms <= 0) return 1;
-  const int base = batch * mla_groups(q_len, mla_pos_per_cta(q_len, slab));  // CTAs before any split
+  const int base = batch * mla_groups(q_len, mla_pos_per_cta(q_len));  // CTAs before any split
   const int tiles = (max_seq_len + 127) / 128;            // 128-token tiles of the longest request
   int parts = sms / base;                                 // fill the GPU once ...
   const int by_length = (tiles + 3) / 4;                  // ... with at least four tiles (512 tokens) per part
@@ -382,10 +399,10 @@ int mla_plan(int batch, int q_len, int max_seq_len, int num_sms, bool slab) {
 }  // namespace
 
 int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms) {
-  return mla_plan(batch, q_len, max_seq_len, num_sms, false);
+  return mla_plan(batch, q_len, max_seq_len, num_sms);
 }
 int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms) {
-  return mla_plan(batch, q_len, seq_len, num_sms, !flags_env_no_tma());
+  return mla_plan(batch, q_len, seq_len, num_sms);
 }
 
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts) {
@@ -424,8 +441,8 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
   p.q_lat = q_lat, p.q_pe = q_pe, p.kv = kv, p.o_lat = o_lat;
   p.seq_lens = seq_lens, p.rows = rows, p.kv_indices = kv_indices, p.kv_indptr = kv_indptr;
   p.batch = batch, p.heads = heads, p.q_len = q_len, p.seq = seq_len;
-  const bool slab = !paged && !flags_env_no_tma();
-  p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len, slab), p.groups = mla_groups(q_len, p.pos_per_cta);
+  const bool slab = !paged;
+  p.parts = parts, p.pos_per_cta = mla_pos_per_cta(q_len), p.groups = mla_groups(q_len, p.pos_per_cta);
   p.kv_format = kv_format, p.scale = scale, p.kv_scale = kv_scale;
   if (slab) {
     int rc = make_kv_slab_map(&p.tm_kv, kv, batch, seq_len, 128);
@@ -438,12 +455,26 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
   const size_t slots = static_cast<size_t>(batch) * p.groups * parts, r = 16u * p.pos_per_cta;
   p.part_ml = reinterpret_cast<float*>(ws + ma::kStatusBytes);
   p.part_o = p.part_ml + slots * r * 2;
-#ifdef MA_TRACE
-  if (std::getenv("MA_NO_MEMSET") == nullptr)
-#endif
   e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes, stream);
   if (e != cudaSuccess) return cuda_rc(e);
   return cuda_rc(ma::launch_mla_decode(p, stream));
+}
+
+int ma_selftest_wait_timeout(uint64_t limit_ns, void* workspace, size_t workspace_bytes, void* stream_) {
+  if (workspace == nullptr) return MA_ERR_NULL_POINTER;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) || workspace_bytes < ma::kStatusBytes) return MA_ERR_WORKSPACE;
+  // The limit is the caller's, but never long: this entry point exists to show that a wait that runs
+  // out ends the kernel, not to occupy an SM.
+  if (limit_ns == 0 || limit_ns > 100ull * 1000ull * 1000ull) return MA_ERR_TOO_LARGE;
+  int dev = 0, major = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  if (e != cudaSuccess) return cuda_rc(e);
+  if (major != 10) return MA_ERR_DEVICE;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes, stream);
+  if (e != cudaSuccess) return cuda_rc(e);
+  return cuda_rc(ma::launch_wait_timeout_selftest(static_cast<uint32_t*>(workspace), limit_ns, stream));
 }
 
 int ma_round_bf16(const float* src, uint16_t* dst, size_t n, int round_mode, void* stream) {

@@ -93,18 +93,6 @@ enum MlaBar : uint32_t {
   kMNumBars = 24
 };
 
-#ifdef MA_TRACE
-// Development-only timestamp trace (built into a separate library, never into the product build).
-__device__ unsigned long long g_trace_mla[8192];
-#define MLA_TRACE_AT(slot, cond)                                                      \
-  do {                                                                                \
-    if ((cond) && blockIdx.x == 0 && (slot) < 8192) g_trace_mla[(slot)] = clock64(); \
-  } while (0)
-#else
-#define MLA_TRACE_AT(slot, cond) \
-  do {                           \
-  } while (0)
-#endif
 
 #define MA_WAIT(bar, parity, site) \
   if (!mbar_wait((bar), (parity), (site), ctx)) return
@@ -214,14 +202,12 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     for (int j = 0; j < w.tiles; ++j) {
       const int st = j % C::kStages;
       if (j >= C::kStages) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / C::kStages) - 1) & 1, 0x50);
-      MLA_TRACE_AT(4000 + j * 4 + 0, j < 60);
       const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
       const uint32_t bar = bars + 8 * (kMTileRaw + st);
       mbar_arrive_expect_tx(bar, kTileBytesMla);
 #pragma unroll
       for (int c = 0; c < 4; ++c) tma_load_3d(tile + c * kChunkBytes, &p.tm_kv, bar, c * 128, (w.tile0 + j) * kTok, w.b);
       tma_load_3d(tile + 4 * kChunkBytes, &p.tm_kv_rope, bar, kLat, (w.tile0 + j) * kTok, w.b);
-      MLA_TRACE_AT(4000 + j * 4 + 1, j < 60);
     }
     return;
   } else {
@@ -254,7 +240,6 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
     const long long slot_mine = slot_next;
     slot_next = slot_of(j + 1);
     if (j >= C::kStages) MA_WAIT_SLEEP(64, bars + 8 * (kMTileEmpty + st), ((j / C::kStages) - 1) & 1, 0x50);
-    MLA_TRACE_AT(4000 + j * 4 + 0, lt == 0 && j < 60);
     const uint32_t tile = base + C::kOffKV + st * kTileBytesMla;
 #pragma unroll
     for (int i = 0; i < kRoundsCopy; ++i) {
@@ -267,7 +252,6 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
                    slot < 0 ? 0u : 16u);
     }
     cp_async_arrive(bars + 8 * (kMTileRaw + st));
-    MLA_TRACE_AT(4000 + j * 4 + 1, lt == 0 && j < 60);
   }
   }
 }
@@ -350,18 +334,14 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
         mbar_test_wait(bars + 8 * (kMTileRaw + (qk_i % C::kStages)), (qk_i / C::kStages) & 1)) {
       if constexpr (!kTma) fence_proxy_async_smem();
       tc_fence_after_sync();
-      MLA_TRACE_AT(2000 + qk_i * 8 + 1, qk_i < 60);
       issue_qk(qk_i, bars + 8 * (kMSFull + (qk_i & 1)));
-      MLA_TRACE_AT(2000 + qk_i * 8 + 2, qk_i < 60);
       ++qk_i;
       progressed = true;
     }
     auto try_pv = [&]() {
       if (pv_i < qk_i && mbar_test_wait(bars + 8 * (kMPFull + (pv_i & 1)), (pv_i >> 1) & 1)) {
         tc_fence_after_sync();
-        MLA_TRACE_AT(2000 + pv_i * 8 + 3, pv_i < 60);
         issue_pv(pv_i);
-        MLA_TRACE_AT(2000 + pv_i * 8 + 4, pv_i < 60);
         ++pv_i;
         progressed = true;
       }
@@ -389,7 +369,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
       const uint64_t now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > ctx.limit_ns) {
         record_error(ctx.status, kErrWaitTimeout, 0x60, (static_cast<uint32_t>(qk_i) << 16) | static_cast<uint32_t>(pv_i));
         *ctx.abort = 1;
         return;
@@ -467,10 +447,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
 
   for (int j = 0; j < n; ++j) {
     const int buf = j & 1, par = (j >> 1) & 1;
-    const bool tr = tid == 0 && j < 60;
-    MLA_TRACE_AT(j * 8 + 0, tr);
     MA_WAIT_WARP(bars + 8 * (kMSFull + buf), par, 0x70);
-    MLA_TRACE_AT(j * 8 + 1, tr);
     tc_fence_after_sync();
     uint32_t d[2 * R];
     ld_pair(tmem + buf * N + lane_sel, d);
@@ -517,9 +494,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       flags[buf * kW + gwarp] = (warp_over ? 1 : 0) | (warp_nan ? 2 : 0);
       mbar_arrive(bars + 8 * (kMFlag + buf));
     }
-    MLA_TRACE_AT(j * 8 + 2, tr);
     MA_WAIT_WARP(bars + 8 * (kMFlag + buf), par, 0x71);
-    MLA_TRACE_AT(j * 8 + 3, tr);
     // overflow is this group's own business, a NaN (the tile is rewritten and multiplied again) everybody's
     int tile_flags = 0;
 #pragma unroll
@@ -637,9 +612,7 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
       const float2 back = from_e4m3x2(t1[r / 2]);
       t2[r / 2] = to_e4m3x2(p0 - back.x, p1 - back.y);
     }
-    MLA_TRACE_AT(j * 8 + 4, tr);
     if (j >= 2) MA_WAIT_WARP(bars + 8 * (kMPvDone + buf), ((j - 2) >> 1) & 1, 0x73);
-    MLA_TRACE_AT(j * 8 + 5, tr);
     uint8_t* pt = smem + C::kOffPT + buf * N * 128;
     if (tl < kTok) {  // the token's 16 first terms and 16 second terms: two 16-byte stores
       *reinterpret_cast<uint4*>(pt + p_off<N>(tl, row0)) =
@@ -695,10 +668,8 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
     fence_proxy_async_smem();
     tc_fence_before_sync();
     mbar_arrive(bars + 8 * (kMPFull + buf));
-    MLA_TRACE_AT(j * 8 + 6, tr);
   }
 
-  MLA_TRACE_AT(5003, tid == 0);
   // epilogue.  With one KV part the CTA finishes its rows itself (normalise, scale back, round to bf16); with
   // several it leaves un-normalised fp32 outputs, reference maxima and denominators for mla_merge_kernel.
   const size_t slot = blockIdx.x;
@@ -769,7 +740,6 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
         part_o[static_cast<size_t>(r) * kLat + mt * 128 + tl] = __uint_as_float(o[r]) + __uint_as_float(o[R + r]);
     }
   }
-  MLA_TRACE_AT(5004, tid == 0);
   if (!direct && tl < R) {
     const float l = (l_part[tl] + l_part[R + tl]) + (l_part[2 * R + tl] + l_part[3 * R + tl]);
     float m = 0.f;
@@ -794,11 +764,7 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const WaitCtx ctx{p.status, abort_flag};
   const Work w = decode_work(p, kPos);
-  MLA_TRACE_AT(5000, tid == 0);
   if (p.parts > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // mla_merge_kernel may line up
-#ifdef MA_TRACE
-  if (tid == 0 && blockIdx.x < 1024) g_trace_mla[6000 + blockIdx.x] = globaltimer_ns();
-#endif
 
   // The query rows are fetched first of all, before any KV copy is on its way: behind three tiles of every CTA
   // (25 MB on the whole GPU) these few loads would wait for microseconds.
@@ -846,7 +812,6 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_slot;
-  MLA_TRACE_AT(5001, tid == 0);
   // The copy warps start fetching at once; the softmax warps first turn the query rows into Q^T.
   // Pools: the copy warps need few registers, the softmax warps many (setmaxnreg, each inside its own branch so
   // that every role is compiled for its own budget).  The warpgroup that holds the MMA warp (descriptors kept in
@@ -922,15 +887,11 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
     fence_proxy_async_smem();
     // every one of these warps gets here unconditionally: a plain named barrier is safe
     asm volatile("bar.sync 1, %0;" ::"n"((kPrepWarps + 1) * 32) : "memory");
-    MLA_TRACE_AT(5002, tid == 0);
     role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
   }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, C::kTmemCols);
-#ifdef MA_TRACE
-  if (tid == 0 && blockIdx.x < 1024) g_trace_mla[7000 + blockIdx.x] = globaltimer_ns();
-#endif
 }
 
 // ---------------------------------------------------------------------------
@@ -1013,11 +974,6 @@ cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
 
 }  // namespace
 
-#ifdef MA_TRACE
-extern "C" int ma_trace_read_mla(unsigned long long* host, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace_mla, sizeof(unsigned long long) * n));
-}
-#endif
 
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
   if (p.pos_per_cta == 2) return p.use_tma ? launch_one<2, true>(p, stream) : launch_one<2, false>(p, stream);

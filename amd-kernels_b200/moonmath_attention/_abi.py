@@ -22,10 +22,12 @@ ROUND_MODE = {"rtne": 0, "rtna": 1, "rtz": 2}
 FLAG_NO_TAIL = 0x1
 FLAG_SIMPLE = 0x2
 FLAG_EXACT_MAX = 0x8
+FLAG_PRECISE_P = 0x10
 FLAG_LITE_PLAIN = 0x20
 
 STATIC_SCRATCH_BYTES = 40 << 20  # MA_STATIC_SCRATCH_BYTES
 ERR_STATIC_SCRATCH = 16
+ERR_FLAGS = 19
 ERR_WAIT_TIMEOUT = 0x57A17  # device status word 0 when a bounded wait gave up
 
 # every symbol include/moonmath_attention.h declares
@@ -39,6 +41,7 @@ EXPORTS = (
     "ma_attention_forward_static",
     "ma_static_status",
     "ma_round_bf16",
+    "ma_selftest_wait_timeout",
     "ma_lite_workspace_bytes",
     "ma_lite_tile",
     "ma_attention_forward_lite",
@@ -76,6 +79,8 @@ def _load() -> ctypes.CDLL:
     lib.ma_attention_forward_static.argtypes = [c_void_p] * 4 + [c_int] * 8 + [c_void_p]
     lib.ma_static_status.restype = c_int
     lib.ma_static_status.argtypes = [c_void_p, c_int, c_void_p]
+    lib.ma_selftest_wait_timeout.restype = c_int
+    lib.ma_selftest_wait_timeout.argtypes = [ctypes.c_uint64, c_void_p, c_size_t, c_void_p]
     lib.ma_round_bf16.restype = c_int
     lib.ma_round_bf16.argtypes = [c_void_p, c_void_p, c_size_t, c_int, c_void_p]
     lib.ma_lite_workspace_bytes.restype = c_size_t

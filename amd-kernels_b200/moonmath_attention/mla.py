@@ -81,15 +81,14 @@ def _launch(who, q_lat, q_pe, kv, o_lat, seq_lens, rows, kv_indices, kv_indptr, 
     with torch.cuda.device(q_lat.device):
         stream = torch.cuda.current_stream(q_lat.device).cuda_stream
         ws_bytes = int(_abi.lib.ma_mla_workspace_bytes(B, q_len, parts))
-        workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q_lat.device)
+        workspace = _kernel._workspace(q_lat.device, ws_bytes)
         rc = _abi.lib.ma_mla_decode_a16w8(
             q_lat.data_ptr(), q_pe.data_ptr(), kv.data_ptr(), o_lat.data_ptr(), ptr(seq_lens), ptr(rows),
             ptr(kv_indices), ptr(kv_indptr), B, H, q_len, seq, parts, float(scale), float(kv_scale), fmt,
-            workspace.data_ptr(), ws_bytes, stream,
+            workspace.data_ptr(), workspace.numel(), stream,
         )
     if rc != 0:
         raise RuntimeError(f"launch_{who} returned error code {rc}: {_abi.error_string(rc)}")
-    _kernel._LAST["workspace"] = workspace
 
 
 def _contiguous(who, multiq, q_lat, q_pe, kv, o_lat, scale, kv_scale):

@@ -20,7 +20,9 @@
  *     256-byte status block that the kernels fill in when a bounded wait gives up;
  *   - the library keeps no state between calls: calls on different streams or
  *     devices may run concurrently (the reference keeps a static schedule,
- *     csrc/attention_kernel.hip:1375-1378).
+ *     csrc/attention_kernel.hip:1375-1378).  The one exception is
+ *     ma_attention_forward_static, which owns a static device array and a
+ *     cached address per device; its comment states the rules.
  *
  * All pointers are device pointers on the current CUDA device; `stream` is a
  * cudaStream_t.  Every call is asynchronous on `stream` and never synchronises.
@@ -52,8 +54,13 @@ extern "C" {
                                     MOONMATH_NO_TAIL, csrc/attention_api.cpp:258-267) */
 #define MA_FLAG_SIMPLE 0x2       /* run the serialised cross-check kernel instead of the pipelined one */
 #define MA_FLAG_EXACT_MAX 0x8    /* rescale the accumulator whenever the running maximum rises (tau = 0) */
+#define MA_FLAG_PRECISE_P 0x10   /* accuracy mode: the softmax probabilities enter the second matrix product as the
+                                    sum of two bf16 terms (16 significant bits instead of the 8 the reference keeps,
+                                    csrc/attention_kernel.hip:446-448), for 25 % more tensor-core work */
 #define MA_FLAG_LITE_PLAIN 0x20  /* ma_attention_forward_lite: hand tasks out in index order, not longest-first
                                     (reference: MOONMATH_LITE_PLAIN / null workspace, csrc/attention_api.cpp:400-407) */
+/* ma_attention_forward(_static) accepts NO_TAIL, SIMPLE, EXACT_MAX and PRECISE_P; ma_attention_forward_lite accepts
+   LITE_PLAIN; any other bit is refused with MA_ERR_FLAGS. */
 
 /* return codes: 1, 2, 3, 5, 6 keep the reference's meaning (csrc/attention_kernel.hip:1573-1576, :1588) */
 #define MA_OK 0
@@ -76,6 +83,7 @@ extern "C" {
 #define MA_ERR_STATIC_SCRATCH 16 /* ma_attention_forward_static: the plan needs more than MA_STATIC_SCRATCH_BYTES */
 #define MA_ERR_LITE_ARGS 17      /* threshold >= 0, phase not 0 / 1, or more than 32766 key blocks of 64 */
 #define MA_ERR_MLA_ARGS 18       /* ma_mla_decode_a16w8: parts or kv_format out of range */
+#define MA_ERR_FLAGS 19          /* a flag bit the entry point does not define */
 #define MA_ERR_CUDA_BASE 1000    /* 1000 + cudaError_t of a failed runtime call or launch */
 
 /* Value of MA_ABI_VERSION the library was built with. */
@@ -139,6 +147,10 @@ int ma_attention_forward(const void* q, const void* k, const void* v, void* out,
  *     launches nothing; with MA_FLAG_NO_TAIL every problem fits (256 bytes are used);
  *   - the first call on each device looks up the array's device address (a host-side set-up step);
  *     make that first call before any stream capture begins;
+ *   - the address is cached per device ordinal for the life of the process.  It belongs to the device's
+ *     primary context as the CUDA runtime sets it up; after cudaDeviceReset the cache is stale (a call that
+ *     then fails with a CUDA error drops it, the next call looks the address up again), and contexts other
+ *     than the primary one are not supported;
  *   - all calls on one device share the one array: calls whose kernels can overlap on the GPU
  *     (different streams, no ordering between them) race on it and must be serialised by the
  *     caller.  Calls ordered on one stream are safe; the array keeps the previous call's contents
@@ -215,6 +227,17 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
                         const int* rows, const int* kv_indices, const int* kv_indptr, int batch, int heads, int q_len,
                         int seq_len, int parts, float scale, float kv_scale, int kv_format, void* workspace,
                         size_t workspace_bytes, void* stream);
+
+/*
+ * Self-test of the failure path: launches one CTA that waits, for at most `limit_ns` (1 .. 100 000 000), on
+ * a barrier nobody arrives on.  The wait gives up, the kernel leaves through its common exit (tensor memory
+ * freed) and returns; nothing faults.  Afterwards (stream drained) the first words of `workspace`
+ * (>= 256 bytes, 256-byte aligned, cleared by this call) read
+ *   [0] 0x57A17 (a bounded wait ran out)   [1] wait site | CTA << 8   [9] 1 (the CTA unwound through its abort flag)
+ * exactly what a production kernel leaves in its status block when a wait times out.  The reference has
+ * no counterpart (it reports through return codes only, csrc/attention_kernel.hip:1573-1576, :1588).
+ */
+int ma_selftest_wait_timeout(uint64_t limit_ns, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * dst[i] = bf16 bits of src[i] under round_mode, NaN -> 0x7FFF; device pointers.

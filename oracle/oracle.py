@@ -192,12 +192,22 @@ def inject_specials(t: torch.Tensor, density: float, seed: int, kinds=(0, 1, 2))
 # ---------------------------------------------------------------------------
 # comparison report
 # ---------------------------------------------------------------------------
-def compare_bits(got: np.ndarray, want: np.ndarray, want_f32: np.ndarray | None = None) -> dict:
+GATE = 2.0 ** -7  # an output counts as "not a cancellation residue" when |oracle| >= GATE * sum_j p_j |v_j| / l
+
+
+def compare_bits(got: np.ndarray, want: np.ndarray, want_f32: np.ndarray | None = None,
+                 row_scale: np.ndarray | None = None) -> dict:
     """Statistics of a bf16 result against the oracle's bf16 bits.
 
     special_mismatch counts positions where either side is NaN/Inf and the bit
     patterns differ (these must be bit- and position-identical); the ULP figures
     cover the positions where both are finite.
+
+    With `row_scale` (= softmax(q k^T / sqrt(D)) @ |v| in fp32, the magnitude the terms of an output had
+    before they cancelled) the report also carries the same histogram restricted to outputs that are not
+    cancellation residues, |oracle| >= GATE * row_scale: `gated_n`, `gated_max_ulp`, `gated_frac_gt1ulp`.
+    An output far below its row scale carries an absolute error that is many units of *its own* last
+    place whatever the kernel does; the gated figures are the ones a precision change moves.
     """
     got = got.reshape(-1)
     want = want.reshape(-1)
@@ -221,4 +231,11 @@ def compare_bits(got: np.ndarray, want: np.ndarray, want_f32: np.ndarray | None 
     err = np.abs(gf.astype(np.float64) - wf.astype(np.float64))
     rep["max_abs_err"] = float(err.max()) if err.size else 0.0
     rep["rmse"] = float(math.sqrt(float((err ** 2).mean()))) if err.size else 0.0
+    if row_scale is not None and want_f32 is not None:
+        scale = np.abs(np.asarray(row_scale, dtype=np.float64).reshape(-1)[fin])
+        keep = np.isfinite(scale) & (np.abs(wf.astype(np.float64)) >= GATE * scale)
+        dg = d[keep]
+        rep["gated_n"] = int(dg.size)
+        rep["gated_max_ulp"] = int(dg.max()) if dg.size else 0
+        rep["gated_frac_gt1ulp"] = float(np.count_nonzero(dg > 1) / max(1, dg.size))
     return rep

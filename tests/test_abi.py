@@ -31,9 +31,9 @@ def test_abi_version_and_error_strings():
     assert _abi.lib.ma_abi_version() == 1
     m = re.search(r"#define MA_ABI_VERSION (\d+)", open(HEADER).read())
     assert int(m.group(1)) == _abi.ABI_VERSION
-    for rc in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 1001):
+    for rc in (0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11, 12, 13, 14, 15, 16, 17, 18, 19, 1001):
         assert _abi.error_string(rc) and "unknown" not in _abi.error_string(rc)
-    assert "unknown" in _abi.error_string(19)
+    assert "unknown" in _abi.error_string(20)
 
 
 def _call(q=16, k=16, v=16, out=16, B=1, H=1, Sq=128, Skv=128, D=128, layout=0, mode=0, ws=0, wsb=0, flags=0):
@@ -51,6 +51,30 @@ def test_argument_validation_return_codes():
     assert _call(q=0) == 9 and _call(out=0) == 9
     assert _call(k=24) == 10
     assert _call(B=70000) == 15
+
+
+def test_undefined_flag_bits_are_refused():
+    """Every flag bit an entry point does not define is an error, not a silent no-op."""
+    header = open(HEADER).read()
+    defined = {name: int(val, 16) for name, val in re.findall(r"#define (MA_FLAG_[A-Z_]+) (0x[0-9a-fA-F]+)", header)}
+    assert defined == {"MA_FLAG_NO_TAIL": 0x1, "MA_FLAG_SIMPLE": 0x2, "MA_FLAG_EXACT_MAX": 0x8,
+                       "MA_FLAG_PRECISE_P": 0x10, "MA_FLAG_LITE_PLAIN": 0x20}
+    assert (_abi.FLAG_NO_TAIL, _abi.FLAG_SIMPLE, _abi.FLAG_EXACT_MAX, _abi.FLAG_PRECISE_P, _abi.FLAG_LITE_PLAIN) == \
+        (0x1, 0x2, 0x8, 0x10, 0x20)
+    for bad in (0x4, 0x20, 0x40, 0x800, 0xB00, 1 << 30):
+        assert _call(flags=bad) == _abi.ERR_FLAGS, hex(bad)
+        assert _abi.lib.ma_attention_forward_static(16, 16, 16, 16, 1, 1, 128, 128, 128, 0, 0, bad, 0) == _abi.ERR_FLAGS
+    lite = lambda flags: _abi.lib.ma_attention_forward_lite(16, 16, 16, 16, 1, 1, 128, 128, 128, 0, 0, 16, 16, None,
+                                                            ctypes.c_float(-3.0), 1, 0, 0, flags, None)
+    assert lite(0x1) == _abi.ERR_FLAGS and lite(0x10) == _abi.ERR_FLAGS and lite(0x20) == 11  # 11: workspace missing
+
+
+def test_selftest_entry_validates_its_arguments():
+    f = _abi.lib.ma_selftest_wait_timeout
+    assert f(1000000, None, 256, None) == 9
+    assert f(1000000, 128, 256, None) == 11          # misaligned
+    assert f(1000000, 256, 64, None) == 11           # too small
+    assert f(0, 256, 256, None) == 15 and f(10**9, 256, 256, None) == 15  # limit out of range
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour of a machine without a GPU")

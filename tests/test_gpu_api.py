@@ -56,6 +56,27 @@ def test_cpu_tensors_are_copied_to_the_gpu_and_back(ma, cuda_device):
     assert torch.equal(out.view(torch.int16), on_gpu.view(torch.int16))
 
 
+@pytest.mark.parametrize("layout,shape", [("bhsd", (2, 6, 1500, 900)), ("bshd", (2, 5, 2100, 700))])
+def test_host_tensor_pipeline_is_bit_identical_to_the_device_path(ma, cuda_device, layout, shape, monkeypatch):
+    """Pinned CPU tensors travel in pieces over three streams (upload, kernel, download).  Each piece is an
+    independent sub-problem made of whole 256-row query blocks, so the result equals the device path's bit for
+    bit when neither splits its last round along KV; `out=` is filled and returned."""
+    monkeypatch.setattr(ma._kernel, "_HOST_CHUNK_BYTES", 256 << 10)  # several pieces per batch at this size
+    B, H, Sq, Skv = shape
+    q, k, v = (t.pin_memory() for t in orc.make_inputs(B, H, Sq, Skv, layout))
+    pieces = ma._kernel._host_chunks(B, H, Sq, layout)
+    assert len(pieces) > 2 * B
+    host_out = torch.empty_like(q).pin_memory()
+    ret = ma.forward(q, k, v, out=host_out, round_mode="rtne", layout=layout)
+    assert ret.data_ptr() == host_out.data_ptr() and ret.device.type == "cpu"
+    monkeypatch.setenv("MOONMATH_NO_TAIL", "1")
+    dev_out = ma.forward(q.to(cuda_device), k.to(cuda_device), v.to(cuda_device), round_mode="rtne", layout=layout).cpu()
+    assert torch.equal(host_out.view(torch.int16), dev_out.view(torch.int16))
+    # pageable tensors take the same route
+    ret2 = ma.forward(q.clone(), k.clone(), v.clone(), round_mode="rtne", layout=layout)
+    assert torch.equal(ret2.view(torch.int16), dev_out.view(torch.int16))
+
+
 def test_runs_on_the_callers_current_stream(ma, cuda_device):
     """Work queued on a side stream before the call must be seen by the kernel (same-stream ordering),
     and the default stream must not need to be involved."""
@@ -143,4 +164,5 @@ def test_randomised_shapes_against_the_oracle(ma):
         torch.cuda.synchronize()
         ref = orc.attention_fp32(q, k, v, layout).numpy()
         wabs = weighted_abs_v(q, k, v, layout).numpy()
-        assert_parity(orc.bf16_tensor_to_bits(out), ref, wabs, mode, f"case {case}: {(B, H, sq, skv, layout, mode)}")
+        assert_parity(orc.bf16_tensor_to_bits(out), ref, wabs, mode, f"case {case}: {(B, H, sq, skv, layout, mode)}",
+                      skv=skv)

@@ -199,6 +199,28 @@ def test_lite_named_blocks_only(ma, cuda_device):
         assert sorted(b for b, _ in lo.walk(write[0, 0, 0].cpu().numpy(), 1 - phase)) == named
 
 
+def test_lite_on_the_reference_tests_own_tensors(ma, cuda_device):
+    """The peaked tensors of the reference's skip-list test, rebuilt and hash-checked against what its generator
+    produced (tests/golden/make_golden_lite.py): after that test's steps at its threshold every list row of head h
+    names exactly h + 1 key blocks (tests/test_attention.py:209-214), and the lists equal the CPU oracle's."""
+    from tests.helpers import reference_peaked_inputs
+
+    got = reference_peaked_inputs()
+    if got is None:
+        pytest.skip("this torch build draws different randn values than the one that made the fixture")
+    q, k, v, g = got
+    B, S, H, _ = q.shape
+    attn = ma.LiteAttention(threshold=float(g["peaked_threshold"]), round_mode="rtna", layout="bshd")
+    dq, dk, dv = (t.to(cuda_device) for t in (q, k, v))
+    for _ in range(int(g["peaked_steps"])):
+        attn(dq, dk, dv)
+    torch.cuda.synchronize()
+    assert ma.last_status()[0] == 0
+    lists = attn.read_list.cpu().numpy()
+    for t in range(lists.shape[2]):
+        assert [lo.kept_blocks(lists[0, h, t]) for h in range(H)] == g["peaked_kept_by_head"].tolist()
+
+
 def test_lite_empty_list_gives_zeros_and_writes_nothing(ma, cuda_device):
     q, k, v = _uniform(cuda_device, "bhsd", 1, 256, 256, 2, seed=5)
     read = torch.zeros(1, 2, 1, 6, dtype=torch.int16, device=cuda_device)

@@ -73,6 +73,43 @@ def _paged_pool(kv, seq_lens, device, seed):
 
 
 # ---- the reference's scenarios ---------------------------------------------------------------------------------
+def test_kernel_against_outputs_of_the_reference_tests_own_formula(ma, cuda_device):
+    """The fixture holds inputs drawn and outputs computed by the reference's own test helpers
+    (tests/test_mla_decode.py:35-96, run by tests/golden/make_golden_mla.py): the kernels are held to the
+    reference's bar (rel-L2 < 3e-3) against those outputs directly, contiguous and through the scattered pool."""
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "mla_reference.npz"))
+    scale, kv_scale, bar = float(g["scale"]), float(g["kv_scale"]), float(g["rel_l2_bar"])
+    bf16 = lambda bits: torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16).to(cuda_device)  # noqa: E731
+    for name in g["cases"]:
+        q_lat, q_pe = bf16(g[f"{name}/q_lat"]), bf16(g[f"{name}/q_pe"])
+        B, q_len, H, _ = q_lat.shape
+        lens = g[f"{name}/seq_lens"].tolist()
+        kv = torch.from_numpy(g[f"{name}/kv"].copy()).view(torch.float8_e4m3fnuz).to(cuda_device)
+        ref = g[f"{name}/ref"]
+        o_lat = torch.zeros_like(q_lat)
+        lens_dev = torch.tensor(lens, dtype=torch.int32, device=cuda_device)
+        if q_len == 1 and lens == [kv.size(1)] * B:
+            ma.mla_decode_a16w8(q_lat[:, 0].contiguous(), q_pe[:, 0].contiguous(), kv, o_lat[:, 0], scale, kv_scale)
+            torch.cuda.synchronize()
+            assert mo.rel_l2(o_lat.float().cpu().numpy(), ref) < bar, name
+        if f"{name}/pool" in g.files:
+            pool = torch.from_numpy(g[f"{name}/pool"].copy()).view(torch.float8_e4m3fnuz).to(cuda_device)
+            slots = torch.from_numpy(g[f"{name}/slots"].copy()).to(cuda_device)
+            indptr = torch.from_numpy(g[f"{name}/indptr"].copy()).to(cuda_device)
+        else:  # a pool in token order: the paged entry points take any q_len in 1..8 and ragged lengths
+            pool = torch.cat([kv[b, :n] for b, n in enumerate(lens)]).unsqueeze(1).contiguous()
+            slots = torch.arange(sum(lens), dtype=torch.int32, device=cuda_device)
+            indptr = torch.tensor([0, *accumulate(lens)], dtype=torch.int32, device=cuda_device)
+        o2 = torch.zeros_like(q_lat)
+        ma.mla_decode_a16w8_paged_dev(q_lat if q_len > 1 else q_lat[:, 0].contiguous(), q_pe if q_len > 1 else q_pe[:, 0].contiguous(),
+                                      pool, o2 if q_len > 1 else o2[:, 0], lens_dev, None, slots, indptr, 1, scale, kv_scale)
+        torch.cuda.synchronize()
+        assert ma.last_status()[0] == 0
+        assert mo.rel_l2(o2.float().cpu().numpy(), ref) < bar, f"{name} paged"
+
+
 @pytest.mark.parametrize("H", [12, 16])
 def test_single_query_matches_reference(ma, cuda_device, H):
     B, S = 2, 2048

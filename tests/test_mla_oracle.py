@@ -45,6 +45,40 @@ def test_oracle_is_the_softmax_formula_of_the_reference_test():
             np.testing.assert_allclose(out[b, t], want.numpy(), rtol=2e-5, atol=1e-6)
 
 
+def _golden():
+    import os
+
+    return np.load(os.path.join(os.path.dirname(__file__), "golden", "mla_reference.npz"))
+
+
+def _bf16_bits_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def test_oracle_reproduces_the_reference_tests_own_formula_on_its_own_inputs():
+    """tests/golden/mla_reference.npz holds inputs drawn by the reference's `_rand_kv` / `_rand_q` and outputs of
+    its `_reference` (tests/test_mla_decode.py:35-68), executed where they lie by tests/golden/make_golden_mla.py:
+    the oracle must agree with them to fp32 noise, ragged lengths and every draft position included."""
+    g = _golden()
+    for name in g["cases"]:
+        out = mo.mla_decode(_bf16_bits_to_f32(g[f"{name}/q_lat"]), _bf16_bits_to_f32(g[f"{name}/q_pe"]), g[f"{name}/kv"],
+                            g[f"{name}/seq_lens"].tolist(), float(g["scale"]), float(g["kv_scale"]))
+        ref = g[f"{name}/ref"]
+        assert out.shape == ref.shape
+        np.testing.assert_allclose(out, ref, rtol=3e-5, atol=2e-6, err_msg=str(name))
+        assert mo.rel_l2(out, ref) < 1e-6
+
+
+def test_pool_gather_reproduces_the_reference_tests_scatter():
+    """`_paged_pool` (tests/test_mla_decode.py:75-96) scatters the rows over a shuffled pool; reading them back
+    through the slot table must give the slab rows again."""
+    g = _golden()
+    lens = g["window/seq_lens"].tolist()
+    rows = mo.gather_pool(g["window/pool"][:, 0], g["window/slots"], g["window/indptr"], lens)
+    for b, n in enumerate(lens):
+        assert np.array_equal(rows[b], g["window/kv"][b, :n])
+
+
 def test_planner_fills_the_gpu_once_and_keeps_parts_long():
     plan = lambda B, q, S: _abi.lib.ma_mla_plan_parts(B, q, S, 148)
     assert plan(148, 1, 4096) == 1 and plan(300, 1, 4096) == 1

@@ -44,7 +44,8 @@ def _worker(rank: int, world: int, port: int, n_slices: int, q):
         t = max_over_ranks(1.0 + rank)
         dist.barrier()
         if rank == 0:
-            q.put((full.view(torch.int16).clone(), t))
+            # plain bytes: a tensor would travel as a shared-memory handle that dies with this process
+            q.put((full.view(torch.int16).numpy().tobytes(), t))
     finally:
         dist.destroy_process_group()
 
@@ -66,4 +67,4 @@ def test_two_ranks_shard_and_gather():
     assert tmax == 2.0  # max over ranks of (1 + rank)
     q, k, v = orc.make_inputs(1, n_slices, 40, 56, "bhsd")
     want = orc.bits_to_bf16_tensor(orc.attention_bf16_bits(q, k, v, "bhsd", "rtne")).view(torch.int16)
-    assert torch.equal(full_bits, want)
+    assert full_bits == want.numpy().tobytes()

@@ -78,6 +78,31 @@ def test_static_scratch_variant_matches_regular_entry_point(abi, cuda_device, ca
     assert np.array_equal(got2, want)
 
 
+def test_static_scratch_variant_allocates_no_device_memory(abi, cuda_device):
+    """What the entry point is for: after its first call on a device (which looks the array's address up),
+    further calls leave the device's free memory exactly where it was -- no cudaMalloc, no pool growth."""
+    B, H, Sq, Skv, layout, mode = 1, 40, 2048, 2048, "bhsd", "rtne"
+    q, k, v = (t.to(cuda_device) for t in orc.make_inputs(B, H, Sq, Skv, layout))
+    out = torch.empty_like(q)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = abi.lib.ma_attention_forward_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), B, H, Sq,
+                                                 Skv, 128, abi.LAYOUT[layout], abi.ROUND_MODE[mode], 0, stream)
+        assert rc == 0, abi.error_string(rc)
+
+    call()  # set-up call
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(cuda_device)
+    reserved_before = torch.cuda.memory_reserved(cuda_device)
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(cuda_device)
+    assert free_after == free_before, (free_before, free_after)
+    assert torch.cuda.memory_reserved(cuda_device) == reserved_before  # torch's allocator was not asked either
+
+
 def test_static_scratch_variant_refuses_plans_beyond_its_buffer(abi, cuda_device):
     """76 tasks x 256 key blocks: the planner wants ~130 MB of partial results; the variant must refuse
     before launching (the tensors are never read), and must accept the same problem without the split."""
