@@ -229,10 +229,16 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// What rounding (lo, hi) to the bf16 pair `packed` left over, again as a bf16 pair: the residual of a
-// round-to-nearest is exactly representable in fp32, so P_hi + P_lo carries p to 16 significant bits.
-__device__ __forceinline__ uint32_t pack_p_residual(float lo, float hi, uint32_t packed) {
-  return pack_p(lo - __uint_as_float(packed << 16), hi - __uint_as_float(packed & 0xFFFF0000u));
+// Precise mode: a probability pair as two bf16 pairs, P_hi + P_lo = p to about 16 significant bits.
+// P_hi is p * (1 - 2^-9) truncated to bf16, so that the remainder p - P_hi is positive for every p > 0
+// (between 2^-9 p and 2^-6.7 p, exact in fp32), and P_lo is that remainder rounded to bf16.  Both terms then have
+// the sign of p: a +-inf in V meets two positive factors and stays +-inf, as in the fp32 formula; a remainder of
+// either sign, or one that is exactly zero, would turn it into NaN (inf - inf, 0 * inf).  p = 0 gives 0 + 0.
+__device__ __forceinline__ void pack_p_precise(float lo, float hi, uint32_t& p_hi, uint32_t& p_lo) {
+  constexpr float kShrink = 1.f - 0.001953125f;  // 1 - 2^-9
+  const uint32_t a = __float_as_uint(lo * kShrink), b = __float_as_uint(hi * kShrink);
+  p_hi = __byte_perm(a, b, 0x7632);  // upper halves: a >> 16 | b & 0xFFFF0000
+  p_lo = pack_p(lo - __uint_as_float(p_hi << 16), hi - __uint_as_float(p_hi & 0xFFFF0000u));
 }
 
 // Address (in elements) of output row `row` of slice (b, h).

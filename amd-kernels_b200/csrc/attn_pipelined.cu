@@ -21,7 +21,7 @@
 // MMAs complete in issue order, which is what makes the S/P aliasing safe.
 //
 // Precise mode (MA_FLAG_PRECISE_P): the probabilities reach the tensor core as the sum of two bf16 terms,
-// P = P_hi + P_lo with P_lo = bf16(p - P_hi), P_hi in columns [0, 64) and P_lo in columns [64, 128) of S_t
+// P = P_hi + P_lo (pack_p_precise), P_hi in columns [0, 64) and P_lo in columns [64, 128) of S_t
 // (all scores are in registers by then), and P*V is issued twice into the same accumulator.  That carries
 // 16 significant bits of p instead of 8 for 25 % more tensor work.
 //
@@ -294,8 +294,11 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
           unpack2(x, x0, x1);
           const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
           sum2[i & 1] = add2(sum2[i & 1], pack2(p0, p1));
-          pk[i] = pack_p(p0, p1);
-          if constexpr (kPrecise) pl[i] = pack_p_residual(p0, p1, pk[i]);
+          if constexpr (kPrecise) {
+            pack_p_precise(p0, p1, pk[i], pl[i]);
+          } else {
+            pk[i] = pack_p(p0, p1);
+          }
         }
         float sa, sb, sc, sd;
         unpack2(sum2[0], sa, sb);
@@ -341,8 +344,11 @@ __device__ __forceinline__ void role_softmax(const AttnParams& p, uint8_t* smem,
           const float p1 = ex2_approx(fmaf(__uint_as_float(s[2 * i + 1]), scale, -m_ref));
           sum0 += p0;
           sum1 += p1;
-          pk[i] = pack_p(p0, p1);
-          if constexpr (kPrecise) pl[i] = pack_p_residual(p0, p1, pk[i]);
+          if constexpr (kPrecise) {
+            pack_p_precise(p0, p1, pk[i], pl[i]);
+          } else {
+            pk[i] = pack_p(p0, p1);
+          }
         }
         l_run += sum0 + sum1;
       }
