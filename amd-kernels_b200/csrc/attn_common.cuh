@@ -219,6 +219,11 @@ __device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
 
 // Packs two probabilities as bf16 for the P operand of the second MMA (`lo` has the lower key index).
 // The tensor core takes A and B of one 16-bit format only: a kind::f16 MMA with fp16 A and bf16 B is
@@ -236,9 +241,14 @@ __device__ __forceinline__ uint32_t pack_p(float lo, float hi) {
 // either sign, or one that is exactly zero, would turn it into NaN (inf - inf, 0 * inf).  p = 0 gives 0 + 0.
 __device__ __forceinline__ void pack_p_precise(float lo, float hi, uint32_t& p_hi, uint32_t& p_lo) {
   constexpr float kShrink = 1.f - 0.001953125f;  // 1 - 2^-9
-  const uint32_t a = __float_as_uint(lo * kShrink), b = __float_as_uint(hi * kShrink);
-  p_hi = __byte_perm(a, b, 0x7632);  // upper halves: a >> 16 | b & 0xFFFF0000
-  p_lo = pack_p(lo - __uint_as_float(p_hi << 16), hi - __uint_as_float(p_hi & 0xFFFF0000u));
+  const f32x2 p2 = pack2(lo, hi);
+  float a, b;
+  unpack2(mul2(p2, pack2(kShrink, kShrink)), a, b);
+  p_hi = __byte_perm(__float_as_uint(a), __float_as_uint(b), 0x7632);  // upper halves: a >> 16 | b & 0xFFFF0000
+  const f32x2 h2 = pack2(__uint_as_float(p_hi << 16), __uint_as_float(p_hi & 0xFFFF0000u));
+  float r0, r1;
+  unpack2(fma2(h2, pack2(-1.f, -1.f), p2), r0, r1);
+  p_lo = pack_p(r0, r1);
 }
 
 // Address (in elements) of output row `row` of slice (b, h).

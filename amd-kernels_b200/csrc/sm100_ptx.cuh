@@ -26,17 +26,6 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
 
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {
@@ -62,19 +51,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 
 // Non-blocking: has the phase with this parity completed?
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
@@ -91,8 +67,9 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Same, but the thread may stay suspended for up to `hint_ns` while the phase is incomplete
-// (it is woken when the phase completes): waiting warps then leave the issue slots to working ones.
+// Has the phase with this parity completed?  The thread may stay suspended for up to `hint_ns` while the
+// phase is incomplete (it is woken when the phase completes): waiting warps then leave the issue slots to
+// working ones.
 __device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
@@ -163,7 +140,8 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 // ---------------------------------------------------------------------------
 // UMMA descriptors
 // ---------------------------------------------------------------------------
-// Shared-memory matrix descriptor (64 bit):
+// Shared-memory matrix descriptor (64 bit; the kernels assemble it from a per-tile low word and a constant
+// high word, see attn_common.cuh):
 //   [ 0,14) start address >> 4        [16,30) leading byte offset >> 4
 //   [32,46) stride byte offset >> 4   [46,48) version = 1 on sm_100
 //   [49,52) base offset (0: tiles are 1024-byte aligned)
@@ -176,15 +154,6 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
 //       SBO = 1024 (distance between groups of 8 K-rows),
 //       LBO = distance between consecutive 64-element MN chunks.
 //       One MMA consumes 16 K-rows = 2048 bytes: advance the start address by 2048.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;  // descriptor version (sm_100)
-  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
-  return d;
-}
 
 // Instruction descriptor for kind::f16 (32 bit):
 //   [4,6) D format (1 = f32)  [7,10) A format  [10,13) B format (0 = f16, 1 = bf16)
@@ -326,7 +295,6 @@ __device__ __forceinline__ void tmem_ld128_sync(uint32_t taddr, uint32_t (&r)[12
       : "r"(taddr), "r"(taddr + 64)
       : "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -372,25 +340,7 @@ __device__ __forceinline__ void tmem_st16x2(uint32_t ta, uint32_t tb, const uint
         "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
-// Variants working on a 32- or 16-register window [kOff, kOff + n) of a larger register array.
-template <int kOff, int kLen>
-__device__ __forceinline__ void tmem_ld32_at(uint32_t taddr, uint32_t (&r)[kLen]) {
-  static_assert(kOff + 32 <= kLen, "window out of range");
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[kOff + 0]), "=r"(r[kOff + 1]), "=r"(r[kOff + 2]), "=r"(r[kOff + 3]), "=r"(r[kOff + 4]), "=r"(r[kOff + 5]), "=r"(r[kOff + 6]), "=r"(r[kOff + 7]), "=r"(r[kOff + 8]), "=r"(r[kOff + 9]), "=r"(r[kOff + 10]), "=r"(r[kOff + 11]), "=r"(r[kOff + 12]), "=r"(r[kOff + 13]), "=r"(r[kOff + 14]), "=r"(r[kOff + 15]), "=r"(r[kOff + 16]), "=r"(r[kOff + 17]), "=r"(r[kOff + 18]), "=r"(r[kOff + 19]), "=r"(r[kOff + 20]), "=r"(r[kOff + 21]), "=r"(r[kOff + 22]), "=r"(r[kOff + 23]), "=r"(r[kOff + 24]), "=r"(r[kOff + 25]), "=r"(r[kOff + 26]), "=r"(r[kOff + 27]), "=r"(r[kOff + 28]), "=r"(r[kOff + 29]), "=r"(r[kOff + 30]), "=r"(r[kOff + 31])
-      : "r"(taddr)
-      : "memory");
-}
-template <int kOff, int kLen>
-__device__ __forceinline__ void tmem_ld_wait32_at(uint32_t (&r)[kLen]) {
-  static_assert(kOff + 32 <= kLen, "window out of range");
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[kOff + 0]), "+r"(r[kOff + 1]), "+r"(r[kOff + 2]), "+r"(r[kOff + 3]), "+r"(r[kOff + 4]), "+r"(r[kOff + 5]), "+r"(r[kOff + 6]), "+r"(r[kOff + 7]), "+r"(r[kOff + 8]), "+r"(r[kOff + 9]), "+r"(r[kOff + 10]), "+r"(r[kOff + 11]), "+r"(r[kOff + 12]), "+r"(r[kOff + 13]), "+r"(r[kOff + 14]), "+r"(r[kOff + 15]), "+r"(r[kOff + 16]), "+r"(r[kOff + 17]), "+r"(r[kOff + 18]), "+r"(r[kOff + 19]), "+r"(r[kOff + 20]), "+r"(r[kOff + 21]), "+r"(r[kOff + 22]), "+r"(r[kOff + 23]), "+r"(r[kOff + 24]), "+r"(r[kOff + 25]), "+r"(r[kOff + 26]), "+r"(r[kOff + 27]), "+r"(r[kOff + 28]), "+r"(r[kOff + 29]), "+r"(r[kOff + 30]), "+r"(r[kOff + 31])
-               :
-               : "memory");
-}
+// Store of a 32-register window [kOff, kOff + 32) of a larger register array.
 template <int kOff, int kLen>
 __device__ __forceinline__ void tmem_st32_at(uint32_t taddr, const uint32_t (&r)[kLen]) {
   static_assert(kOff + 32 <= kLen, "window out of range");
