@@ -5,7 +5,10 @@ Same shapes, input patterns and timing method as the reference's benchmark
 BSHD layout, preallocated `out=`, 8 warm-ups, 30 iterations between two CUDA
 events, median of 5 passes; TFLOP/s = 4*B*H*S^2*D / t.  The AITER / Modular MAX
 columns of the reference cannot be reproduced (AMD software); its own published
-milliseconds are printed for comparison.
+milliseconds are printed for comparison.  The reference also prints, per mode, the largest
+absolute difference and the rmse between its output and AITER's (benchmark/runner.py:214-222);
+here the same two figures are taken against fp32 attention computed with torch on the GPU
+(TF32 off) over 1024 sample query rows of the last (batch, head) slice.
 
     python amd-kernels_b200/bench_table.py [--pattern realistic] [--shapes std,long] [--passes 5]
 """
@@ -96,6 +99,22 @@ def time_passes(fn, warmup: int, iters: int, passes: int) -> float:
     return samples[len(samples) // 2]
 
 
+def accuracy_sample(out, q, k, v):
+    """(max |diff|, rmse) of `out` against fp32 softmax(q k^T / sqrt(D)) v on the first and last 512 query rows of
+    the last (batch, head) slice; all tensors (B, S, H, D)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        S, D = q.size(1), q.size(3)
+        rows = torch.cat([torch.arange(0, min(512, S)), torch.arange(max(0, S - 512), S)]).unique().to(q.device)
+        qf, kf, vf = q[-1, rows, -1].float(), k[-1, :, -1].float(), v[-1, :, -1].float()
+        ref = torch.softmax(qf @ kf.t() / (D ** 0.5), dim=-1) @ vf
+        d = (out[-1, rows, -1].float() - ref).abs()
+        return d.max().item(), d.pow(2).mean().sqrt().item()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--pattern", default="realistic", choices=PATTERNS)
@@ -117,8 +136,9 @@ def main() -> None:
     dev = torch.device("cuda:0")
     want = set(a.shapes.split(","))
     rows = []
-    print(f"| shape (B,H,S,D) | mode | B200 ms | TFLOP/s | % of {peak or '?'} | MI300X ms (reference) | speed-up |")
-    print("|---|---|---|---|---|---|---|")
+    print(f"| shape (B,H,S,D) | mode | B200 ms | TFLOP/s | % of {peak or '?'} | MI300X ms (reference) | speed-up | "
+          "max abs diff | rmse |")
+    print("|---|---|---|---|---|---|---|---|---|")
     for label, B, H, S, D in SHAPES:
         if label not in want:
             continue
@@ -129,13 +149,15 @@ def main() -> None:
             ms = time_passes(lambda: ma.forward(q, k, v, out=out, round_mode=mode, layout="bshd"),
                              a.warmup, a.iters, a.passes)
             status = ma.last_status()[0]
+            max_abs, rmse = accuracy_sample(out, q, k, v)
             tf = flops / ms / 1e9
             ref_ms = REFERENCE_MS[label][mi]
             rows.append(dict(label=label, shape=[B, H, S, D], mode=mode, ms=ms, tflops=tf, ref_ms=ref_ms,
-                             status=status, pattern=a.pattern))
+                             status=status, pattern=a.pattern, max_abs=max_abs, rmse=rmse))
             frac = f"{100 * tf / peak:.1f}" if peak else "-"
             print(f"| {label} ({B},{H},{S},{D}) | {mode} | {ms:.3f} | {tf:.0f} | {frac} | {ref_ms:.3f} | "
-                  f"{ref_ms / ms:.2f}x |" + ("" if status == 0 else f" status {status:#x}"), flush=True)
+                  f"{ref_ms / ms:.2f}x | {max_abs:.2e} | {rmse:.2e} |" + ("" if status == 0 else f" status {status:#x}"),
+                  flush=True)
         del q, k, v, out
         torch.cuda.empty_cache()
     if a.json:

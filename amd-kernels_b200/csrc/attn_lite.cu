@@ -335,41 +335,104 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
           if (i >= valid1) s[64 + i] = __float_as_uint(-INFINITY);
         }
       }
-      const float m0 = half_max(s) * scale, m1 = half_max(s + 64) * scale;
-
-      // Votes (reference: hip:981-993).  The first processed block of a task is always kept; its successor in
-      // the same step is judged against the maximum the first block establishes.
       const bool first = j == 0;
-      const float ref1 = first ? ((m0 == -INFINITY) ? 0.f : m0) : m_ref;
-      const bool want0 = live && (m0 - m_ref) > thr;
-      const bool want1 = live && sb.b1 >= 0 && (m1 - ref1) > thr;
-      const bool keep0 = first || __any_sync(0xffffffffu, want0);
-      const bool keep1 = __any_sync(0xffffffffu, want1);
-      if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
-      if (!keep0 || !keep1) {
-        // A skipping warp contributes nothing for the block and its state does not see it.
+      uint32_t pk[64];
+      bool exact = first;
+      if (!first) {
+        // Speculative sweep, as in the dense kernel: exponentiate against the reference maximum as it stands and
+        // read the votes off the two half sums instead of looking for the half maxima first.  With 64 keys,
+        // max <= log2(sum) <= max + 6 (all in units relative to the reference), so
+        //   log2(sum) <= threshold      : no row of this half can ask to keep it          -> the vote is "skip",
+        //   log2(sum) >  threshold + 6  : this row's maximum is above the threshold        -> the vote is "keep",
+        // and both verdicts equal what the exact maxima would give.  Anything in between, a sum that might move
+        // the reference maximum (> 2^tau), or a NaN / inf, sends the warp to the exact path below; nothing has
+        // been stored by then.  The lower bound needs the exponentials not to flush to zero (x >= -126), which
+        // holds for every key within a threshold above -100; thresholds below that take "skip" from the exact
+        // path only.
+        const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
+        f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          if (!keep0) s[i] = __float_as_uint(-INFINITY);
-          if (!keep1) s[64 + i] = __float_as_uint(-INFINITY);
+          const f32x2 x = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
+          float x0, x1;
+          unpack2(x, x0, x1);
+          const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+          sum2[i >> 5] = add2(sum2[i >> 5], pack2(p0, p1));
+          pk[i] = pack_p(p0, p1);
+        }
+        float sa, sb2, sc, sd;
+        unpack2(sum2[0], sa, sb2);
+        unpack2(sum2[1], sc, sd);
+        const float sum_h0 = sa + sb2, sum_h1 = sc + sd;
+        const float l0 = lg2_approx(sum_h0), l1 = lg2_approx(sum_h1);  // -inf for an absent or fully masked half
+        constexpr float kSlack = 1.f / 1024.f;  // covers the approximate exponentials, logarithm and the fp32 sums
+        const bool moves = !(sum_h0 + sum_h1 <= 255.f);  // the block maximum may exceed the reference by tau = 8 (or NaN)
+        uint32_t bits = moves ? 16u : 0u;
+        if (live) {
+          bits |= (l0 > thr + 6.f + kSlack ? 1u : 0u) | (l0 > thr - kSlack ? 2u : 0u);
+          if (sb.b1 >= 0) bits |= (l1 > thr + 6.f + kSlack ? 4u : 0u) | (l1 > thr - kSlack ? 8u : 0u);
+        }
+        bits = __reduce_or_sync(0xffffffffu, bits);
+        const bool keep0 = (bits & 1u) != 0u, keep1 = (bits & 4u) != 0u;
+        const bool skip_ok = thr > -100.f;
+        if ((bits & 16u) != 0u || (!keep0 && ((bits & 2u) != 0u || !skip_ok)) ||
+            (!keep1 && ((bits & 8u) != 0u || (!skip_ok && sb.b1 >= 0)))) {
+          exact = true;
+          tmem_ld128_sync(tS, s);
+          if (valid0 < kLiteKeyBlock || valid1 < kLiteKeyBlock) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+              if (i >= valid0) s[i] = __float_as_uint(-INFINITY);
+              if (i >= valid1) s[64 + i] = __float_as_uint(-INFINITY);
+            }
+          }
+        } else {
+          if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
+          // A skipping warp contributes nothing for the block and its state does not see it.
+          if (!keep0) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) pk[i] = 0u;
+          }
+          if (!keep1) {
+#pragma unroll
+            for (int i = 32; i < 64; ++i) pk[i] = 0u;
+          }
+          l_run += (keep0 ? sum_h0 : 0.f) + (keep1 ? sum_h1 : 0.f);
         }
       }
-      const float m_blk = fmaxf(keep0 ? m0 : -INFINITY, keep1 ? m1 : -INFINITY);
-      if (first) {
-        m_ref = (m_blk == -INFINITY) ? 0.f : m_blk;
-      } else {
-        const bool need = (m_blk - m_ref) > p.a.rescale_tau;
-        if (__any_sync(0xffffffffu, need)) {
-          const float m_new = fmaxf(m_ref, m_blk);
-          const float alpha = ex2_approx(m_ref - m_new);
-          m_ref = m_new;
-          l_run *= alpha;
-          rescale_accumulator(tO, alpha);
+      if (exact) {
+        const float m0 = half_max(s) * scale, m1 = half_max(s + 64) * scale;
+
+        // Votes (reference: hip:981-993).  The first processed block of a task is always kept; its successor in
+        // the same step is judged against the maximum the first block establishes.
+        const float ref1 = first ? ((m0 == -INFINITY) ? 0.f : m0) : m_ref;
+        const bool want0 = live && (m0 - m_ref) > thr;
+        const bool want1 = live && sb.b1 >= 0 && (m1 - ref1) > thr;
+        const bool keep0 = first || __any_sync(0xffffffffu, want0);
+        const bool keep1 = __any_sync(0xffffffffu, want1);
+        if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
+        if (!keep0 || !keep1) {
+          // A skipping warp contributes nothing for the block and its state does not see it.
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            if (!keep0) s[i] = __float_as_uint(-INFINITY);
+            if (!keep1) s[64 + i] = __float_as_uint(-INFINITY);
+          }
         }
-      }
-      // p = 2^(s * scale - m_ref), two keys per FMA / add instruction; the row sum uses the unrounded values
-      uint32_t pk[64];
-      {
+        const float m_blk = fmaxf(keep0 ? m0 : -INFINITY, keep1 ? m1 : -INFINITY);
+        if (first) {
+          m_ref = (m_blk == -INFINITY) ? 0.f : m_blk;
+        } else {
+          const bool need = (m_blk - m_ref) > p.a.rescale_tau;
+          if (__any_sync(0xffffffffu, need)) {
+            const float m_new = fmaxf(m_ref, m_blk);
+            const float alpha = ex2_approx(m_ref - m_new);
+            m_ref = m_new;
+            l_run *= alpha;
+            rescale_accumulator(tO, alpha);
+          }
+        }
+        // p = 2^(s * scale - m_ref), two keys per FMA / add instruction; the row sum uses the unrounded values
         const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
         f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
@@ -381,10 +444,10 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
           sum2[i & 1] = add2(sum2[i & 1], pack2(p0, p1));
           pk[i] = pack_p(p0, p1);
         }
-        float sa, sb, sc, sd;
-        unpack2(sum2[0], sa, sb);
+        float sa, sb2, sc, sd;
+        unpack2(sum2[0], sa, sb2);
         unpack2(sum2[1], sc, sd);
-        l_run += (sa + sb) + (sc + sd);
+        l_run += (sa + sb2) + (sc + sd);
       }
       tmem_st32_at<0>(tS, pk);
       tmem_st32_at<32>(tS + 32, pk);
