@@ -294,7 +294,7 @@ def forward(
             the second matrix product, as the reference does (csrc/attention_kernel.hip:446-448).
             True (or MOONMATH_PRECISE_P=1): they are carried as the sum of two bf16 terms, which brings
             the result to within one bf16 unit of the fp32 formula wherever the output is not a
-            cancellation residue; costs about a quarter more time.
+            cancellation residue; costs about 40 % more time.
 
     Returns:
         torch.bfloat16 tensor of the same shape and device as q. The kernel is
