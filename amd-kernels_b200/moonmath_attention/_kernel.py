@@ -205,7 +205,7 @@ def _host_chunks(B: int, H: int, Sq: int, layout: str) -> list[tuple]:
 
 
 def _forward_host(q, k, v, out, round_mode: str, layout: str, flags: int | None):
-    """CPU tensors in, CPU tensor out, arithmetic on cuda:0 (the reference's convenience,
+    """CPU tensors in, CPU tensor out, arithmetic on the current CUDA device (the reference's convenience,
     moonmath_attention/_kernel.py:52-67, which copies q, k, v up, runs, and copies the result down, one
     after the other).  Here the three legs overlap: the problem is cut into independent pieces
     (`_host_chunks`); one stream uploads, a second runs the kernel on each piece as soon as its inputs have
@@ -214,7 +214,9 @@ def _forward_host(q, k, v, out, round_mode: str, layout: str, flags: int | None)
     pageable ones work, more slowly.  The result is complete when the call returns.  `out`, if given, is
     filled and returned (the reference ignores a CPU `out` and returns a new tensor)."""
     B, H, Sq, Skv = _check_problem(q, k, v, out, round_mode, layout)
-    device = torch.device("cuda", 0)
+    # The reference says "cuda:0"; the current device is that in a single-GPU process, and the right one in a
+    # process that was given its own GPU with torch.cuda.set_device (one rank per GPU).
+    device = torch.device("cuda", torch.cuda.current_device())
     if flags is None:
         flags = _flags_from_env()
     # The pieces never split their last round along KV: their kernels hide under the copies anyway, and a
@@ -283,8 +285,9 @@ def forward(
         q, k, v: torch.bfloat16 tensors of shape (batch, heads, seq_len, head_dim)
                  or (batch, seq_len, heads, head_dim) depending on layout.
                  Contiguous. head_dim=128. K and V may have their own length.
-                 CPU tensors are copied to cuda:0 and the result is copied back
-                 (a convenience copy; the arithmetic always runs on the GPU).
+                 CPU tensors are copied to the current CUDA device (cuda:0 unless the process
+                 selected another) and the result is copied back (a convenience copy; the
+                 arithmetic always runs on the GPU).
         out: optional preallocated output tensor. Must match q's shape, dtype,
              device, and be contiguous. If None, a new tensor is allocated.
         round_mode: "rtna" (default; ties away from zero), "rtne", or "rtz"
