@@ -114,6 +114,35 @@ def test_concurrent_calls_on_two_streams_do_not_interfere(ma, cuda_device):
         assert torch.equal(got_b.view(torch.int16), want_b.view(torch.int16))
 
 
+def test_workspaces_are_kept_per_stream_and_status_follows_the_stream(ma, cuda_device):
+    """The package reuses one workspace per (device, stream, thread): calls on one stream share it (ordered, so
+    safe), two streams never do, and `last_status()` reads the block of the current stream's latest call."""
+    a = [t.to(cuda_device) for t in orc.make_inputs(1, 40, 2048, 2048, "bhsd")]   # plan with a KV-split tail
+    b = [t.to(cuda_device) for t in orc.make_inputs(1, 3, 300, 300, "bhsd", base=3)]
+    want_a, want_b = ma.forward(*a, round_mode="rtne"), ma.forward(*b, round_mode="rtne")
+    torch.cuda.synchronize()
+    ws = ma._kernel._WORKSPACES
+    key_default = ma._kernel._slot_key(cuda_device)
+    assert key_default in ws
+    big = ws[key_default].data_ptr()
+    ma.forward(*b, round_mode="rtne")                      # a smaller problem on the same stream: same buffer
+    assert ws[key_default].data_ptr() == big
+    side = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(side):
+        got_a = ma.forward(*a, round_mode="rtne")
+        key_side = ma._kernel._slot_key(cuda_device)
+        assert key_side != key_default and ws[key_side].data_ptr() != big
+        # interleave: the default stream runs the other problem while the side stream's call is in flight
+        with torch.cuda.stream(torch.cuda.default_stream(cuda_device)):
+            got_b = ma.forward(*b, round_mode="rtne")
+        assert ma.last_status()[0] == 0                    # the side stream's block
+    torch.cuda.synchronize()
+    assert ma.last_status()[0] == 0                        # the default stream's block
+    assert torch.equal(got_a.view(torch.int16), want_a.view(torch.int16))
+    assert torch.equal(got_b.view(torch.int16), want_b.view(torch.int16))
+    assert len(ws) <= ma._kernel._WORKSPACE_SLOTS
+
+
 def test_forward_and_lite_replay_from_a_cuda_graph(ma, cuda_device, monkeypatch):
     """The dense call (memset, main kernel and, where the plan splits the last wave, merge; 240 tasks here) and a
     LiteAttention call keep no host state between launches: captured once, they replay bit-identically on new data."""
