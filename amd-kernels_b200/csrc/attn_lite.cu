@@ -310,6 +310,8 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
     }
     StepBlocks hist1{-1, -1, false, false}, hist2{-1, -1, false, false};  // steps j - 1 and j - 2
     float m_ref = 0.f, l_run = 0.f;
+    constexpr float kSlack = 1.f / 1024.f;
+    const float sum_keep = ex2_approx(thr + 6.f + kSlack), sum_skip = ex2_approx(thr - kSlack);
     for (int j = 0; j < n; ++j, ++blk) {
       StepBlocks sb{-1, -1, false, false};
       sb.b0 = cur.block;
@@ -319,9 +321,6 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
 
       MA_WAIT_WARP_SLEEP(kSleepSoftmax, bar_s, blk & 1, 0x30 + tile);
       tc_fence_after_sync();
-      // S(j) of tile 0 follows P V (j-1) of tile 0 in the MMA order, which follows P V (j-2) of tile 1:
-      // every warp's votes of step j - 2 are in shared memory.
-      if (emits && j >= 2) rec.step(hist2, verdict + ((blk - 2) % kVerdictRing) * 8, false);
 
       uint32_t s[128];
       tmem_ld128_sync(tS, s);
@@ -350,27 +349,28 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
         // holds for every key within a threshold above -100; thresholds below that take "skip" from the exact
         // path only.
         const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
-        f32x2 sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
+        f32x2 sum2[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};  // two per half
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
           const f32x2 x = fma2(pack2(__uint_as_float(s[2 * i]), __uint_as_float(s[2 * i + 1])), scale2, negm2);
           float x0, x1;
           unpack2(x, x0, x1);
           const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-          sum2[i >> 5] = add2(sum2[i >> 5], pack2(p0, p1));
+          sum2[(i >> 5) * 2 + (i & 1)] = add2(sum2[(i >> 5) * 2 + (i & 1)], pack2(p0, p1));
           pk[i] = pack_p(p0, p1);
         }
         float sa, sb2, sc, sd;
-        unpack2(sum2[0], sa, sb2);
-        unpack2(sum2[1], sc, sd);
+        unpack2(add2(sum2[0], sum2[1]), sa, sb2);
+        unpack2(add2(sum2[2], sum2[3]), sc, sd);
         const float sum_h0 = sa + sb2, sum_h1 = sc + sd;
-        const float l0 = lg2_approx(sum_h0), l1 = lg2_approx(sum_h1);  // -inf for an absent or fully masked half
-        constexpr float kSlack = 1.f / 1024.f;  // covers the approximate exponentials, logarithm and the fp32 sums
+        // The thresholds are compared in the linear domain: log2(sum) > t  <=>  sum > 2^t (both bounds computed
+        // once per task; 2^-1000 is 0, so "sum > 0" then).  kSlack widens the undecided band by what the
+        // approximate exponentials and the fp32 sums can be off.
         const bool moves = !(sum_h0 + sum_h1 <= 255.f);  // the block maximum may exceed the reference by tau = 8 (or NaN)
         uint32_t bits = moves ? 16u : 0u;
         if (live) {
-          bits |= (l0 > thr + 6.f + kSlack ? 1u : 0u) | (l0 > thr - kSlack ? 2u : 0u);
-          if (sb.b1 >= 0) bits |= (l1 > thr + 6.f + kSlack ? 4u : 0u) | (l1 > thr - kSlack ? 8u : 0u);
+          bits |= (sum_h0 > sum_keep ? 1u : 0u) | (sum_h0 > sum_skip ? 2u : 0u);
+          if (sb.b1 >= 0) bits |= (sum_h1 > sum_keep ? 4u : 0u) | (sum_h1 > sum_skip ? 8u : 0u);
         }
         bits = __reduce_or_sync(0xffffffffu, bits);
         const bool keep0 = (bits & 1u) != 0u, keep1 = (bits & 4u) != 0u;
@@ -454,6 +454,11 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
+      // The list entry of step j - 2, written off the critical path (the thread has until the next S arrives).
+      // S(j) of tile 0 followed P V (j-1) of tile 0 in the MMA order, which followed P V (j-2) of tile 1: every
+      // warp's votes of step j - 2 are in shared memory, and no warp can be at step j + 2 yet (that needs this
+      // tile's P of step j + 1), so the slot has not been reused.
+      if (emits && j >= 2) rec.step(hist2, verdict + ((blk - 2) % kVerdictRing) * 8, false);
       hist2 = hist1;
       hist1 = sb;
     }
