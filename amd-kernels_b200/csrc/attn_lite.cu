@@ -311,7 +311,7 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
     StepBlocks hist1{-1, -1, false, false}, hist2{-1, -1, false, false};  // steps j - 1 and j - 2
     float m_ref = 0.f, l_run = 0.f;
     constexpr float kSlack = 1.f / 1024.f;
-    const float sum_keep = ex2_approx(thr + 6.f + kSlack), sum_skip = ex2_approx(thr - kSlack);
+    const float sum_keep = ex2_approx(thr + 6.f + kSlack);
     for (int j = 0; j < n; ++j, ++blk) {
       StepBlocks sb{-1, -1, false, false};
       sb.b0 = cur.block;
@@ -341,13 +341,10 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
         // Speculative sweep, as in the dense kernel: exponentiate against the reference maximum as it stands and
         // read the votes off the two half sums instead of looking for the half maxima first.  With 64 keys,
         // max <= log2(sum) <= max + 6 (all in units relative to the reference), so
-        //   log2(sum) <= threshold      : no row of this half can ask to keep it          -> the vote is "skip",
-        //   log2(sum) >  threshold + 6  : this row's maximum is above the threshold        -> the vote is "keep",
-        // and both verdicts equal what the exact maxima would give.  Anything in between, a sum that might move
-        // the reference maximum (> 2^tau), or a NaN / inf, sends the warp to the exact path below; nothing has
-        // been stored by then.  The lower bound needs the exponentials not to flush to zero (x >= -126), which
-        // holds for every key within a threshold above -100; thresholds below that take "skip" from the exact
-        // path only.
+        //   log2(sum) > threshold + 6  : this row's maximum is above the threshold  ->  the vote is "keep",
+        // exactly what the exact maxima would give.  A half no row is certain about, a sum that might move the
+        // reference maximum (> 2^tau), or a NaN / inf, sends the warp to the exact path below; nothing has been
+        // stored by then.
         const f32x2 scale2 = pack2(scale, scale), negm2 = pack2(-m_ref, -m_ref);
         f32x2 sum2[4] = {pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};  // two per half
 #pragma unroll
@@ -363,20 +360,18 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
         unpack2(add2(sum2[0], sum2[1]), sa, sb2);
         unpack2(add2(sum2[2], sum2[3]), sc, sd);
         const float sum_h0 = sa + sb2, sum_h1 = sc + sd;
-        // The thresholds are compared in the linear domain: log2(sum) > t  <=>  sum > 2^t (both bounds computed
-        // once per task; 2^-1000 is 0, so "sum > 0" then).  kSlack widens the undecided band by what the
-        // approximate exponentials and the fp32 sums can be off.
+        // The threshold is compared in the linear domain: log2(sum) > t  <=>  sum > 2^t (computed once per task;
+        // 2^-1000 is 0, so "sum > 0" then).  kSlack covers what the approximate exponentials and the fp32 sums
+        // can be off.
         const bool moves = !(sum_h0 + sum_h1 <= 255.f);  // the block maximum may exceed the reference by tau = 8 (or NaN)
         uint32_t bits = moves ? 16u : 0u;
-        if (live) {
-          bits |= (sum_h0 > sum_keep ? 1u : 0u) | (sum_h0 > sum_skip ? 2u : 0u);
-          if (sb.b1 >= 0) bits |= (sum_h1 > sum_keep ? 4u : 0u) | (sum_h1 > sum_skip ? 8u : 0u);
-        }
+        if (live) bits |= (sum_h0 > sum_keep ? 1u : 0u) | (sb.b1 >= 0 && sum_h1 > sum_keep ? 4u : 0u);
         bits = __reduce_or_sync(0xffffffffu, bits);
+        // The sweep's result stands only when every half that exists is certainly kept: a half some warp skips
+        // has to be taken out of P and of the row sum, which the exact path below does (it is the rarer case: a
+        // skipped block leaves the list).  An absent second half has scores of -inf, p = 0 and sum 0 already.
         const bool keep0 = (bits & 1u) != 0u, keep1 = (bits & 4u) != 0u;
-        const bool skip_ok = thr > -100.f;
-        if ((bits & 16u) != 0u || (!keep0 && ((bits & 2u) != 0u || !skip_ok)) ||
-            (!keep1 && ((bits & 8u) != 0u || (!skip_ok && sb.b1 >= 0)))) {
+        if ((bits & 16u) != 0u || !keep0 || (!keep1 && sb.b1 >= 0)) {
           exact = true;
           tmem_ld128_sync(tS, s);
           if (valid0 < kLiteKeyBlock || valid1 < kLiteKeyBlock) {
@@ -387,17 +382,8 @@ __device__ __forceinline__ void role_softmax(const LiteParams& p, uint8_t* smem,
             }
           }
         } else {
-          if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = (keep0 ? 0u : 1u) | (keep1 ? 0u : 2u);
-          // A skipping warp contributes nothing for the block and its state does not see it.
-          if (!keep0) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) pk[i] = 0u;
-          }
-          if (!keep1) {
-#pragma unroll
-            for (int i = 32; i < 64; ++i) pk[i] = 0u;
-          }
-          l_run += (keep0 ? sum_h0 : 0.f) + (keep1 ? sum_h1 : 0.f);
+          if (lane0) verdict[(blk % kVerdictRing) * 8 + warp8] = keep1 ? 0u : 2u;
+          l_run += sum_h0 + sum_h1;
         }
       }
       if (exact) {
