@@ -231,8 +231,6 @@ def _forward_host(q, k, v, out, round_mode: str, layout: str, flags: int | None)
             s.wait_stream(caller)
         dq, dk, dv = (torch.empty(t.shape, dtype=t.dtype, device=device) for t in (q, k, v))
         dout = torch.empty(q.shape, dtype=q.dtype, device=device)
-        sent = torch.cuda.Event()
-        done = torch.cuda.Event()
         last_batch = -1
         for piece in _host_chunks(B, H, Sq, layout):
             b, lo, hi = piece
