@@ -68,3 +68,47 @@ def test_two_ranks_shard_and_gather():
     q, k, v = orc.make_inputs(1, n_slices, 40, 56, "bhsd")
     want = orc.bits_to_bf16_tensor(orc.attention_bf16_bits(q, k, v, "bhsd", "rtne")).view(torch.int16)
     assert full_bits == want.numpy().tobytes()
+
+
+def _failing_worker(rank: int, world: int, port: int, q):
+    """Rank 1 leaves between steps (after the rendezvous, before the exchange); rank 0 must learn of it as an error."""
+    import datetime
+
+    import torch.distributed as dist
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for p in (root, os.path.join(root, "amd-kernels_b200")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from moonmath_attention.shard import gather_slices
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    dist.barrier()
+    if rank == 1:
+        os._exit(3)  # no collective of this rank is in flight
+    local = torch.zeros(1, 3, 4, 128, dtype=torch.bfloat16)
+    try:
+        gather_slices(local, 5)
+        q.put("gathered")
+    except Exception as e:  # noqa: BLE001  (whatever the backend raises for a lost peer or a timeout)
+        q.put("error: " + type(e).__name__)
+    os._exit(0)  # the process group cannot be torn down cleanly without its peer
+
+
+def test_a_rank_that_leaves_is_reported_not_waited_for():
+    """Failure detection on the host (the device side has none to inject): the exchange with a rank that is gone
+    ends in an exception within the process-group timeout instead of hanging."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = 31500 + (os.getpid() % 2000)
+    procs = [ctx.Process(target=_failing_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    verdict = queue.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+    assert verdict.startswith("error"), verdict
+    assert procs[1].exitcode == 3 and procs[0].exitcode == 0
