@@ -83,6 +83,7 @@ struct MlaParams {
   float* part_ml;         // [B * groups * parts][16 * pos_per_cta][2] reference maximum (log2 units), denominator
   int batch, heads, q_len, seq;
   int parts, groups, pos_per_cta;
+  int cluster_merge;      // set by the launcher: the parts of a request form a thread-block cluster and merge through shared memory
   int kv_format;          // 0: e4m3-fnuz (the reference's), 1: e4m3 (OCP, what the tensor core reads)
   float scale, kv_scale;
 };

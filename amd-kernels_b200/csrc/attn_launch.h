@@ -31,6 +31,9 @@ cudaError_t launch_lite_order(const LiteParams& p, int* order, cudaStream_t stre
 
 // MLA absorbed decode: one CTA per (request, group of draft positions, KV part), then the merge of the parts.
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream);
+// Clusters of `parts` decode CTAs (2..8) that the current device holds at once; 0: no such cluster.  A request's
+// parts are launched as one cluster, and merged through shared memory, while batch x groups is within this.
+int mla_cluster_capacity(int pos_per_cta, bool slab, int parts);
 
 // One CTA that waits, under `limit_ns`, on a barrier nobody arrives on: exercises the time-out branch of the
 // bounded waits, the status words and the unwind that frees tensor memory.  `status`: 64 zeroed words.

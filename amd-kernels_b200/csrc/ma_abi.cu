@@ -405,6 +405,11 @@ int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms)
   return mla_plan(batch, q_len, seq_len, num_sms);
 }
 
+int ma_mla_cluster_capacity(int q_len, int paged, int parts) {
+  if (q_len < 1 || q_len > 8) return 0;
+  return ma::mla_cluster_capacity(mla_pos_per_cta(q_len), paged == 0, parts);
+}
+
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts) {
   if (batch <= 0 || q_len < 1 || q_len > 8 || parts < 1) return ma::kStatusBytes;
   // one slot of 16 rows per (request, position, part); positions are rounded up to even, which also covers

@@ -24,10 +24,16 @@
 // by hand, so the result is exact for up to 640 such entries per tile of 96 tokens (beyond that the rest stay
 // at +-224).  0x80 (NaN there) reads as zero.  e4m3 caches (kv_format 1) are read unchanged.
 //
-// One CTA per (request, group of draft positions, KV part); parts are merged by mla_merge_kernel.
+// One CTA per (request, group of draft positions, KV part).  Up to eight parts of a request form a thread-block
+// cluster: each leaves its partial result in its own shared memory and, after a cluster barrier, merges a share
+// of the rows from all of them (distributed shared memory, no trip through L2, no second launch).  More parts
+// (a few long requests) go through global memory and mla_merge_kernel.
 //   warps 0-3  softmax / rescale / epilogue    warp 4  MMA issuer    warps 5-12 (or 5)  copy
 // All waits are bounded mbarrier waits.
 #include <cuda_fp8.h>
+
+#include <atomic>
+#include <type_traits>
 
 #include "attn_common.cuh"
 #include "attn_launch.h"
@@ -68,6 +74,10 @@ struct Cfg {
   static constexpr int kStages = 3;
   static constexpr int kSatCap = kPos == 1 ? 640 : 256;         // saturated e4m3-fnuz entries of one tile that are corrected exactly
   static constexpr uint32_t kOffKV = 0;
+  // After the last P V the stages are idle; a part of a cluster leaves its result there for the merge:
+  // float [kRows][512] un-normalised outputs, then float2 [kRows] (reference maximum, denominator).
+  static constexpr uint32_t kOffPartO = kOffKV;
+  static constexpr uint32_t kOffPartMl = kOffPartO + kRows * kLat * 4;
   static constexpr uint32_t kOffQT = kStages * kTileBytesMla;       // [5 chunks][kN rows][128 B]
   static constexpr uint32_t kOffPT = kOffQT + kChunks * kN * 128;      // [2][128 token rows][kN B], kN-byte swizzle (96 rows used)
   static constexpr uint32_t kOffRowScale = kOffPT + 2 * kN * 128;      // float [kRows]: score = (S1 + S2) * this
@@ -671,11 +681,14 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   }
 
   // epilogue.  With one KV part the CTA finishes its rows itself (normalise, scale back, round to bf16); with
-  // several it leaves un-normalised fp32 outputs, reference maxima and denominators for mla_merge_kernel.
+  // several it leaves un-normalised fp32 outputs, reference maxima and denominators: in its own shared memory
+  // for the merge inside the cluster (cluster_merge below), else in global memory for mla_merge_kernel.
   const size_t slot = blockIdx.x;
-  float* part_o = p.part_o + (slot * RT + row0) * kLat;  // this group's 16 rows of the CTA's slot
-  float2* part_ml = reinterpret_cast<float2*>(p.part_ml) + slot * RT + row0;
-  const bool direct = p.parts == 1;
+  const bool direct = p.parts == 1, in_smem = p.cluster_merge != 0;
+  float* part_o = in_smem ? reinterpret_cast<float*>(smem + C::kOffPartO) + row0 * kLat
+                          : p.part_o + (slot * RT + row0) * kLat;  // this group's 16 rows
+  float2* part_ml = in_smem ? reinterpret_cast<float2*>(smem + C::kOffPartMl) + row0
+                            : reinterpret_cast<float2*>(p.part_ml) + slot * RT + row0;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat);
   auto out_row = [&](int r) {  // row r of this group: its position, head r
     return ((static_cast<size_t>(w.brow) * w.q_len + w.pos0 + group) * w.heads + r) * kLat;
@@ -750,6 +763,94 @@ __device__ __forceinline__ void role_softmax(const MlaParams& p, const Work& w, 
   }
 }
 
+// ---------------------------------------------------------------------------
+// merge inside a cluster: the P parts of a request are the CTAs of one thread-block cluster; each has left its
+// partial result in its own shared memory (role_softmax) and all have passed a cluster barrier.  Part c finishes
+// head rows c, c + P, ... of every position of the CTA: out = sum_q 2^(m_q - M) O_q / sum_q 2^(m_q - M) l_q,
+// scaled back, rounded to bf16.  A thread takes four dimensions of a row; the loads of a chunk of rows from all
+// parts (at most 16 x 16 bytes and 16 x 8 bytes per thread) are issued together.
+// ---------------------------------------------------------------------------
+template <int kPos, int P>
+__device__ __forceinline__ void cluster_merge_rows(const MlaParams& p, const Work& w, uint32_t base, int tid) {
+  using C = Cfg<kPos>;
+  constexpr int R = kHeadsMax, kRowsMax = (R + P - 1) / P, kChunk = R / P;
+  static_assert(P >= 2 && P <= 8 && kChunk >= 2, "cluster of two to eight parts");
+  const int group = tid >> 7, tl = tid & 127;
+  if (w.pos0 + group >= w.q_len) return;  // a position past the window has no output rows
+  uint32_t o_at[P], ml_at[P];
+#pragma unroll
+  for (int q = 0; q < P; ++q) {
+    const uint32_t there = cluster_map(base, q);
+    o_at[q] = there + C::kOffPartO + (group * R * kLat + tl * 4) * 4;
+    ml_at[q] = there + C::kOffPartMl + group * R * 8;
+  }
+  const float scale_back = p.kv_scale / (p.kv_format == 0 ? 2.f : 1.f);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat) +
+                       (static_cast<size_t>(w.brow) * w.q_len + w.pos0 + group) * w.heads * kLat + tl * 4;
+  auto part_live = [](float2 v) { return v.y > 0.f || v.y != v.y; };  // a part without tokens has denominator 0
+#pragma unroll
+  for (int k0 = 0; k0 < kRowsMax; k0 += kChunk) {
+    float2 ml[kChunk][P];
+    float4 o[kChunk][P];
+#pragma unroll
+    for (int k = 0; k < kChunk; ++k) {
+      const int r = w.part + (k0 + k) * P;
+      const bool row = k0 + k < kRowsMax && r < w.heads;  // uniform over the CTA
+#pragma unroll
+      for (int q = 0; q < P; ++q) {
+        ml[k][q] = make_float2(-INFINITY, 0.f);
+        o[k][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row) {
+          ml[k][q] = ld_cluster_f32x2(ml_at[q] + r * 8);
+          o[k][q] = ld_cluster_f32x4(o_at[q] + r * (kLat * 4));  // never written by a part without tokens: not used then
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kChunk; ++k) {
+      const int r = w.part + (k0 + k) * P;
+      if (!(k0 + k < kRowsMax && r < w.heads)) continue;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < P; ++q)
+        if (part_live(ml[k][q])) m_all = fmaxf(m_all, ml[k][q].x);
+      float l_all = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int q = 0; q < P; ++q) {
+        if (!part_live(ml[k][q])) continue;
+        const float wgt = ex2_approx(ml[k][q].x - m_all);
+        l_all += wgt * ml[k][q].y;
+        acc.x += wgt * o[k][q].x, acc.y += wgt * o[k][q].y, acc.z += wgt * o[k][q].z, acc.w += wgt * o[k][q].w;
+      }
+      const float inv = (l_all > 0.f || l_all != l_all) ? scale_back / l_all : 0.f;
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2*>(out + static_cast<size_t>(r) * kLat) =
+          make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+  }
+}
+
+__device__ __forceinline__ void cluster_sync() {
+  __syncwarp();
+  cluster_arrive_release();
+  cluster_wait_acquire();
+}
+
+template <int kPos>
+__device__ __forceinline__ void cluster_merge(const MlaParams& p, const Work& w, uint32_t base, int tid) {
+  switch (p.parts) {
+    case 2: cluster_merge_rows<kPos, 2>(p, w, base, tid); break;
+    case 3: cluster_merge_rows<kPos, 3>(p, w, base, tid); break;
+    case 4: cluster_merge_rows<kPos, 4>(p, w, base, tid); break;
+    case 5: cluster_merge_rows<kPos, 5>(p, w, base, tid); break;
+    case 6: cluster_merge_rows<kPos, 6>(p, w, base, tid); break;
+    case 7: cluster_merge_rows<kPos, 7>(p, w, base, tid); break;
+    case 8: cluster_merge_rows<kPos, 8>(p, w, base, tid); break;
+    default: break;
+  }
+}
+
 template <int kPos, bool kTma>
 __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kernel(const __grid_constant__ MlaParams p) {
   using C = Cfg<kPos>;
@@ -764,7 +865,7 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const WaitCtx ctx{p.status, abort_flag};
   const Work w = decode_work(p, kPos);
-  if (p.parts > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // mla_merge_kernel may line up
+  if (p.parts > 1 && !p.cluster_merge) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // mla_merge_kernel may line up
 
   // The query rows are fetched first of all, before any KV copy is on its way: behind three tiles of every CTA
   // (25 MB on the whole GPU) these few loads would wait for microseconds.
@@ -888,8 +989,20 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
     // every one of these warps gets here unconditionally: a plain named barrier is safe
     asm volatile("bar.sync 1, %0;" ::"n"((kPrepWarps + 1) * 32) : "memory");
     role_softmax<kPos>(p, w, smem, base, tmem, tid, ctx);
+    if (p.cluster_merge) {
+      // Every thread of every part of the request passes two cluster barriers, also after a wait that gave up (its
+      // role returned): the first says that all partial results lie in shared memory, the second that nobody reads
+      // this CTA's shared memory any more.  Between them the softmax warps merge (here, with their register budget).
+      cluster_sync();
+      cluster_merge<kPos>(p, w, base, tid);
+      cluster_sync();
+    }
   }
   tc_fence_before_sync();
+  if (p.cluster_merge && warp >= kMmaWarp) {  // the softmax warps' two barriers: see their branch above
+    cluster_sync();
+    cluster_sync();
+  }
   __syncthreads();
   if (warp == kMmaWarp) tmem_dealloc(tmem, C::kTmemCols);
 }
@@ -950,30 +1063,130 @@ __global__ void __launch_bounds__(kMergeWarps * 32) mla_merge_kernel(const MlaPa
   *reinterpret_cast<uint2*>(out) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
 }
 
+// The same for up to eight parts that could not be one cluster (more requests than the device holds clusters of
+// that size): one CTA of 128 threads per output row, a thread four dimensions, all parts' loads issued together,
+// so that the whole merge is one wave of CTAs and one trip to L2.
+constexpr int kMergeFewParts = 8;
+__global__ void __launch_bounds__(128) mla_merge_few_kernel(const MlaParams p, int kpos) {
+  const int R = kHeadsMax * kpos;
+  const int row = blockIdx.x;  // (b, pos, h)
+  const int h = row % p.heads, pos = (row / p.heads) % p.q_len, b = row / (p.heads * p.q_len);
+  const int brow = p.rows != nullptr ? p.rows[b] : b;
+  const int group = pos / kpos, r = (pos % kpos) * kHeadsMax + h;
+  const size_t slot0 = (static_cast<size_t>(b) * p.groups + group) * p.parts;
+  const float2* ml = reinterpret_cast<const float2*>(p.part_ml);
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // the decode grid has completed and its partials are visible
+  float2 v[kMergeFewParts];
+  float4 o[kMergeFewParts];
+#pragma unroll
+  for (int q = 0; q < kMergeFewParts; ++q) {
+    const size_t at = (slot0 + (q < p.parts ? q : 0)) * R + r;  // a part without tokens never wrote its outputs: read, not used
+    v[q] = ml[at];
+    o[q] = *reinterpret_cast<const float4*>(p.part_o + at * kLat + threadIdx.x * 4);
+    if (q >= p.parts) v[q] = make_float2(-INFINITY, 0.f);
+  }
+  auto live = [](float2 x) { return x.y > 0.f || x.y != x.y; };
+  float m_all = -INFINITY;
+#pragma unroll
+  for (int q = 0; q < kMergeFewParts; ++q)
+    if (live(v[q])) m_all = fmaxf(m_all, v[q].x);
+  float l_all = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int q = 0; q < kMergeFewParts; ++q) {
+    if (!live(v[q])) continue;
+    const float wgt = ex2_approx(v[q].x - m_all);
+    l_all += wgt * v[q].y;
+    acc.x += wgt * o[q].x, acc.y += wgt * o[q].y, acc.z += wgt * o[q].z, acc.w += wgt * o[q].w;
+  }
+  const float fmt = p.kv_format == 0 ? 2.f : 1.f;
+  const float inv = l_all > 0.f || l_all != l_all ? p.kv_scale / (fmt * l_all) : 0.f;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.o_lat) +
+                       ((static_cast<size_t>(brow) * p.q_len + pos) * p.heads + h) * kLat + threadIdx.x * 4;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv), hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+  *reinterpret_cast<uint2*>(out) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+constexpr int kClusterPartsMax = 8;  // the portable cluster size
+
+// How many clusters of `parts` CTAs of this kernel the device holds at once (0: such a cluster cannot be launched).
+// Asked once per device and size.
 template <int kPos, bool kTma>
-cudaError_t launch_one(const MlaParams& p, cudaStream_t stream) {
+int active_clusters(int parts, size_t smem_bytes) {
+  constexpr int kDevices = 64;
+  static std::atomic<int> known[kDevices][kClusterPartsMax + 1];  // answer + 1; 0: not asked yet
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kDevices) return 0;
+  const int have = known[dev][parts].load(std::memory_order_relaxed);
+  if (have != 0) return have - 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(parts), cfg.blockDim = dim3(block_threads(kTma, kPos)), cfg.dynamicSmemBytes = smem_bytes;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = parts, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaFuncSetAttribute(mla_decode_kernel<kPos, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(smem_bytes)) != cudaSuccess ||
+      cudaOccupancyMaxActiveClusters(&n, mla_decode_kernel<kPos, kTma>, &cfg) != cudaSuccess) {
+    (void)cudaGetLastError();
+    n = 0;
+  }
+  known[dev][parts].store(n + 1, std::memory_order_relaxed);
+  return n;
+}
+
+template <int kPos, bool kTma>
+cudaError_t launch_one(const MlaParams& params, cudaStream_t stream) {
   using C = Cfg<kPos>;
   constexpr size_t smem_bytes = C::kOffBars + kMNumBars * 8 + 1024;
   static_assert(smem_bytes <= 232448, "shared memory budget of one CTA on sm_100");
+  static_assert(C::kOffPartMl + C::kRows * 8 <= C::kStages * kTileBytesMla, "a part's result fits the idle stages");
   cudaError_t e = cudaFuncSetAttribute(mla_decode_kernel<kPos, kTma>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        static_cast<int>(smem_bytes));
   if (e != cudaSuccess) return e;
-  mla_decode_kernel<kPos, kTma><<<p.batch * p.groups * p.parts, block_threads(kTma, kPos), smem_bytes, stream>>>(p);
-  e = cudaGetLastError();
-  if (e != cudaSuccess || p.parts == 1) return e;  // a single part writes the final output itself
+  MlaParams p = params;
+  // The parts of a request as one cluster, when all clusters of the call are resident together (a cluster that
+  // had to wait for a free group of SMs would cost more than the merge kernel does).
+  p.cluster_merge = p.parts >= 2 && p.parts <= kClusterPartsMax &&
+                    p.batch * p.groups <= active_clusters<kPos, kTma>(p.parts, smem_bytes);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(p.batch * p.groups * p.parts), cfg.blockDim = dim3(block_threads(kTma, kPos));
+  cfg.dynamicSmemBytes = smem_bytes, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = p.cluster_merge ? p.parts : 1, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, mla_decode_kernel<kPos, kTma>, p);
+  if (e != cudaSuccess || p.parts == 1 || p.cluster_merge) return e;  // the decode kernel has written the final output itself
   // The merge is launched as a programmatic dependent: its CTAs may take their places while the parts still
   // run (they are small enough to sit beside a decode CTA) and wait there for the decode grid to complete.
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(p.batch * p.q_len * p.heads * 4), cfg.blockDim = dim3(kMergeWarps * 32), cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, mla_merge_kernel, p, static_cast<int>(kPos));
+  const bool few = p.parts <= kMergeFewParts;
+  cudaLaunchConfig_t mcfg = {};
+  mcfg.gridDim = dim3(p.batch * p.q_len * p.heads * (few ? 1 : 4)), mcfg.blockDim = dim3(few ? 128 : kMergeWarps * 32);
+  mcfg.stream = stream;
+  cudaLaunchAttribute mattr[1];
+  mattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  mattr[0].val.programmaticStreamSerializationAllowed = 1;
+  mcfg.attrs = mattr, mcfg.numAttrs = 1;
+  return few ? cudaLaunchKernelEx(&mcfg, mla_merge_few_kernel, p, static_cast<int>(kPos))
+             : cudaLaunchKernelEx(&mcfg, mla_merge_kernel, p, static_cast<int>(kPos));
 }
 
 }  // namespace
 
+
+int mla_cluster_capacity(int pos_per_cta, bool slab, int parts) {
+  if (parts < 2 || parts > kClusterPartsMax) return 0;
+  auto ask = [&](auto kpos, auto tma) {
+    using C = Cfg<decltype(kpos)::value>;
+    return active_clusters<decltype(kpos)::value, decltype(tma)::value>(parts, C::kOffBars + kMNumBars * 8 + 1024);
+  };
+  using One = std::integral_constant<int, 1>;
+  using Two = std::integral_constant<int, 2>;
+  if (pos_per_cta == 2) return slab ? ask(Two{}, std::true_type{}) : ask(Two{}, std::false_type{});
+  return slab ? ask(One{}, std::true_type{}) : ask(One{}, std::false_type{});
+}
 
 cudaError_t launch_mla_decode(const MlaParams& p, cudaStream_t stream) {
   if (p.pos_per_cta == 2) return p.use_tma ? launch_one<2, true>(p, stream) : launch_one<2, false>(p, stream);

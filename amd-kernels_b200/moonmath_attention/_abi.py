@@ -48,6 +48,7 @@ EXPORTS = (
     "ma_mla_plan_parts",
     "ma_mla_plan_parts_contiguous",
     "ma_mla_workspace_bytes",
+    "ma_mla_cluster_capacity",
     "ma_mla_decode_a16w8",
 )
 
@@ -97,6 +98,8 @@ def _load() -> ctypes.CDLL:
     lib.ma_mla_plan_parts_contiguous.argtypes = [c_int] * 4
     lib.ma_mla_workspace_bytes.restype = c_size_t
     lib.ma_mla_workspace_bytes.argtypes = [c_int] * 3
+    lib.ma_mla_cluster_capacity.restype = c_int
+    lib.ma_mla_cluster_capacity.argtypes = [c_int] * 3
     lib.ma_mla_decode_a16w8.restype = c_int
     lib.ma_mla_decode_a16w8.argtypes = (
         [c_void_p] * 8 + [c_int] * 5 + [ctypes.c_float, ctypes.c_float, c_int, c_void_p, c_size_t, c_void_p]

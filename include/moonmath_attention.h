@@ -223,6 +223,12 @@ int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
 /* The split the contiguous entry points of the Python package choose for themselves (same rule). */
 int ma_mla_plan_parts_contiguous(int batch, int q_len, int seq_len, int num_sms);
 size_t ma_mla_workspace_bytes(int batch, int q_len, int parts);
+/* With 2..8 parts, the parts of a request run as one thread-block cluster and merge their results through
+ * shared memory, as long as all clusters of the call are resident at once: batch x ceil(q_len / 2) (batch when
+ * q_len = 1) <= this number, which depends on the device, the cluster size and the kernel variant (paged: 0 for
+ * a contiguous cache, 1 for a pool).  Otherwise, and with more parts, a merge kernel follows.  Results are the
+ * same either way up to fp32 summation order.  0: no GPU, or no such cluster.  No counterpart in the reference. */
+int ma_mla_cluster_capacity(int q_len, int paged, int parts);
 int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, void* o_lat, const int* seq_lens,
                         const int* rows, const int* kv_indices, const int* kv_indptr, int batch, int heads, int q_len,
                         int seq_len, int parts, float scale, float kv_scale, int kv_format, void* workspace,

@@ -206,7 +206,7 @@ def test_single_query_ragged_lengths_and_few_heads(ma, cuda_device, B, H, S):
 
 
 @pytest.mark.parametrize("q_len", [1, 2, 3, 6, 7])
-@pytest.mark.parametrize("parts", [1, 3, 64, 256])
+@pytest.mark.parametrize("parts", [1, 3, 8, 64, 256])
 def test_paged_every_window_length_and_split(ma, cuda_device, q_len, parts):
     B, H = 2, 16
     seq_lens = [700, 1301]
@@ -216,6 +216,36 @@ def test_paged_every_window_length_and_split(ma, cuda_device, q_len, parts):
     lens = torch.tensor(seq_lens, dtype=torch.int32, device=cuda_device)
     ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
     _check(ma, o_lat, _oracle(q_lat, q_pe, kv, seq_lens), f"paged q_len {q_len} parts {parts}")
+
+
+@pytest.mark.parametrize("parts", [2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("q_len", [1, 4])
+def test_parts_merged_inside_a_cluster_and_by_the_merge_kernel_agree(ma, cuda_device, parts, q_len):
+    """Two to eight parts of a request run as one thread-block cluster and merge through shared memory while the
+    device holds all clusters of the call at once; with more requests than that a merge kernel follows.  Both
+    ways, on the same ragged requests (some parts of the short ones are empty), against the oracle; the two
+    outputs may differ by the fp32 summation order only."""
+    from moonmath_attention import _abi
+
+    H = 16 if q_len == 1 else 8
+    groups = 1 if q_len == 1 else (q_len + 1) // 2
+    capacity = _abi.lib.ma_mla_cluster_capacity(q_len, 1, parts)
+    assert 1 <= capacity <= 148 // parts
+    few, many = 3, capacity // groups + 1       # requests: inside one wave of clusters / one more than fit
+    seq_lens = [97 + 211 * (b % 7) for b in range(many)]
+    kv = _rand_kv(many, max(seq_lens), cuda_device, 61)
+    q_lat, q_pe, o_lat = _rand_q(many, q_len if q_len > 1 else None, H, cuda_device, 61)
+    pool, kv_indices, kv_indptr = _paged_pool(kv, seq_lens, cuda_device, 61)
+    lens = torch.tensor(seq_lens, dtype=torch.int32, device=cuda_device)
+    ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, kv_indices, kv_indptr, parts, SCALE, KV_SCALE)
+    ref = _oracle(q_lat, q_pe, kv, seq_lens)
+    _check(ma, o_lat, ref, f"merge kernel, parts {parts} q_len {q_len}")
+    o_few = torch.zeros_like(o_lat[:few])
+    ma.mla_decode_a16w8_paged_dev(q_lat[:few].contiguous(), q_pe[:few].contiguous(), pool, o_few, lens[:few].contiguous(), None,
+                                  kv_indices, kv_indptr[:few + 1].contiguous(), parts, SCALE, KV_SCALE)
+    _check(ma, o_few, ref[:few], f"cluster, parts {parts} q_len {q_len}")
+    diff = (o_few.float() - o_lat[:few].float()).abs().max().item()
+    assert diff <= 2.0 ** -7 * o_lat[:few].float().abs().max().item()   # a bf16 rounding step at most
 
 
 def test_e4m3_cache_is_read_unchanged(ma, cuda_device):
