@@ -95,6 +95,7 @@ struct WaitCtx {
   uint32_t* status;     // global status block or null
   volatile int* abort;  // shared-memory flag: some thread of this CTA gave up
   uint64_t limit_ns = kWaitLimitNs;  // how long one wait may last before it is abandoned
+  bool watch_status = true;  // give up as soon as any CTA has reported an error (needs a status word that was zero before the launch)
 };
 
 __device__ __forceinline__ void record_error(uint32_t* status, uint32_t code, uint32_t site, uint32_t detail) {
@@ -129,7 +130,7 @@ __device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, ui
     if (kSleepNs > 0) asm volatile("nanosleep.u32 %0;" ::"n"(kSleepNs));
     if ((it & 0x3Fu) == 0u) {
       if (*ctx.abort) return false;
-      if (ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
+      if (ctx.watch_status && ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
         *ctx.abort = 1;
         return false;
       }

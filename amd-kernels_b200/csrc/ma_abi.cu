@@ -460,8 +460,8 @@ int ma_mla_decode_a16w8(const void* q_lat, const void* q_pe, const void* kv, voi
   const size_t slots = static_cast<size_t>(batch) * p.groups * parts, r = 16u * p.pos_per_cta;
   p.part_ml = reinterpret_cast<float*>(ws + ma::kStatusBytes);
   p.part_o = p.part_ml + slots * r * 2;
-  e = cudaMemsetAsync(workspace, 0, ma::kStatusBytes, stream);
-  if (e != cudaSuccess) return cuda_rc(e);
+  // (the status word is cleared by the kernel itself: a memset in front of it would cost two microseconds and
+  // keep the kernel from lining up behind its predecessor in the stream)
   return cuda_rc(ma::launch_mla_decode(p, stream));
 }
 

@@ -372,7 +372,7 @@ __device__ __forceinline__ void role_mma(const Work& w, uint8_t* smem, uint32_t 
       t0 = 0;
     } else if ((++idle & 0x3FFu) == 0u) {  // bounded like every other wait
       if (*ctx.abort) return;
-      if (ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
+      if (ctx.watch_status && ctx.status != nullptr && *reinterpret_cast<volatile uint32_t*>(ctx.status) != 0u) {
         *ctx.abort = 1;
         return;
       }
@@ -863,13 +863,46 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
   __shared__ int abort_flag_s;
   volatile int* abort_flag = &abort_flag_s;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const WaitCtx ctx{p.status, abort_flag};
+  // Errors of other CTAs are not watched: the status word is cleared by CTA 0 of this launch (below), not before it.
+  const WaitCtx ctx{p.status, abort_flag, kWaitLimitNs, false};
+  // Programmatic dependent launch, in both directions.  The kernel behind this one in the stream may take its
+  // places as SMs become free (a decode call behind a decode call: one CTA per SM, so a CTA of the next call
+  // moves in when the one before it leaves; a merge kernel: beside the decode CTAs).  And this kernel sets up
+  // barriers and tensor memory while the kernel before it still runs, then waits for it to complete before it
+  // touches global memory: the queries, the cache, the lengths and the status word may all be its results.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  constexpr int kMmaWarp = 4 * kPos, kFirstCopyWarp = kMmaWarp + 1;  // softmax warps, MMA warp, copy warps
+  if (tid < static_cast<int>(kMNumBars)) {  // one barrier per thread
+    const uint32_t i = tid;
+    uint32_t count = 1;
+    if (i >= kMTileRaw && i < kMTileRaw + kMaxStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
+    if (i >= kMPFull && i < kMPFull + 2) count = kPos * kSoftmaxThreads;
+    if ((i >= kMMx && i < kMMx + 4) || (i >= kMEpi && i < kMEpi + 2)) count = 4;
+    if ((i >= kMFlag && i < kMFlag + 2) || (i >= kMSat && i < kMSat + 2) || i == kMRedoReq) count = 4 * kPos;
+    mbar_init(base + C::kOffBars + 8 * i, count);
+    if (i == 0) abort_flag_s = 0;
+    if (i < 4) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  if constexpr (kTma) {
+    if (tid == kFirstCopyWarp * 32) {  // the thread that issues the box loads: their descriptors are kernel parameters
+      tma_prefetch_desc(&p.tm_kv);
+      tma_prefetch_desc(&p.tm_kv_rope);
+    }
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const Work w = decode_work(p, kPos);
-  if (p.parts > 1 && !p.cluster_merge) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // mla_merge_kernel may line up
+  // The status word of the call: errors are recorded by compare-and-swap against zero, and the first of them
+  // comes after a wait has run out, long after this store.  (Nobody watches the word for other CTAs' errors:
+  // a CTA whose wait runs out ends by itself.)
+  if (blockIdx.x == 0 && tid == 0) *reinterpret_cast<volatile uint32_t*>(p.status) = 0u;
 
   // The query rows are fetched first of all, before any KV copy is on its way: behind three tiles of every CTA
-  // (25 MB on the whole GPU) these few loads would wait for microseconds.
-  constexpr int kMmaWarp = 4 * kPos, kFirstCopyWarp = kMmaWarp + 1;  // softmax warps, MMA warp, copy warps
+  // (25 MB on the whole GPU) these few loads would wait for microseconds.  All are issued before the barrier below.
   const __nv_bfloat16* q_lat = static_cast<const __nv_bfloat16*>(p.q_lat);
   const __nv_bfloat16* q_pe = static_cast<const __nv_bfloat16*>(p.q_pe);
   constexpr int kPrepWarps = kMmaWarp;  // the softmax warps
@@ -892,22 +925,6 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
         vin[k][i] = x < kLat ? *reinterpret_cast<const uint4*>(q_lat + qrow * kLat + x)
                              : *reinterpret_cast<const uint4*>(q_pe + qrow * 64 + (x - kLat));
     }
-  }
-  if (tid < static_cast<int>(kMNumBars)) {  // one barrier per thread
-    const uint32_t i = tid;
-    uint32_t count = 1;
-    if (i >= kMTileRaw && i < kMTileRaw + kMaxStagesMla) count = kTma ? 1u : static_cast<uint32_t>(kCopyThreads);
-    if (i >= kMPFull && i < kMPFull + 2) count = kPos * kSoftmaxThreads;
-    if ((i >= kMMx && i < kMMx + 4) || (i >= kMEpi && i < kMEpi + 2)) count = 4;
-    if ((i >= kMFlag && i < kMFlag + 2) || (i >= kMSat && i < kMSat + 2) || i == kMRedoReq) count = 4 * kPos;
-    mbar_init(base + C::kOffBars + 8 * i, count);
-    if (i == 0) abort_flag_s = 0;
-    if (i < 4) reinterpret_cast<int*>(smem + C::kOffSatCnt)[i] = 0;
-    mbar_fence_init();
-  }
-  if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
-    tmem_relinquish();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -1153,10 +1170,12 @@ cudaError_t launch_one(const MlaParams& params, cudaStream_t stream) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(p.batch * p.groups * p.parts), cfg.blockDim = dim3(block_threads(kTma, kPos));
   cfg.dynamicSmemBytes = smem_bytes, cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = p.cluster_merge ? p.parts : 1, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr, cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // see the head of the kernel
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 2;
   e = cudaLaunchKernelEx(&cfg, mla_decode_kernel<kPos, kTma>, p);
   if (e != cudaSuccess || p.parts == 1 || p.cluster_merge) return e;  // the decode kernel has written the final output itself
   // The merge is launched as a programmatic dependent: its CTAs may take their places while the parts still

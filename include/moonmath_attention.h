@@ -217,6 +217,10 @@ int ma_attention_forward_lite(const void* q, const void* k, const void* v, void*
  *     read as it is; a NaN code in it reaches both draft positions of the CTA that reads the row (positions are
  *     processed in pairs), also the one whose causal limit lies before that token.
  *   parts: KV split per request, 1..MA_MLA_MAX_PARTS (ma_mla_plan_parts); workspace: ma_mla_workspace_bytes.
+ *   Stream order: the kernel is launched as a programmatic dependent of whatever kernel precedes it in the stream
+ *     (it sets up while that kernel drains, then waits for it to complete before it reads or writes global
+ *     memory), and it lets a kernel launched the same way behind it do the same.  No memset precedes it: the
+ *     first word of the status block is cleared by the kernel.
  */
 #define MA_MLA_MAX_PARTS 256
 int ma_mla_plan_parts(int batch, int q_len, int max_seq_len, int num_sms);
