@@ -1027,13 +1027,15 @@ __global__ void __launch_bounds__(block_threads(kTma, kPos), 1) mla_decode_kerne
 // ---------------------------------------------------------------------------
 // merge of the KV parts: out = sum_p 2^(m_p - M) O_p / sum_p 2^(m_p - M) l_p, scaled back, rounded to bf16
 // ---------------------------------------------------------------------------
-// One CTA per (output row, quarter of the 512 dimensions); its eight warps take every eighth part, a lane four
-// dimensions (16-byte loads), and the warps' sums meet in shared memory.
-constexpr int kMergeWarps = 8;
-__global__ void __launch_bounds__(kMergeWarps * 32) mla_merge_kernel(const MlaParams p, int kpos) {
+// One CTA per (output row, quarter of the 512 dimensions); its warps (8, or 32 for more than 64 parts) take every
+// n-th part, a lane four dimensions (16-byte loads), and the warps' sums meet in shared memory.  With 148 parts of
+// one long request every warp then has at most five parts, whose loads are issued together: two trips to L2 (the
+// maxima, then the rows) instead of six.
+constexpr int kMergeWarps = 8, kMergeWarpsMany = 32;
+__global__ void __launch_bounds__(kMergeWarpsMany * 32) mla_merge_kernel(const MlaParams p, int kpos) {
   const int R = kHeadsMax * kpos;
   const int row = blockIdx.x >> 2, quarter = blockIdx.x & 3;  // row = (b, pos, h)
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
   const int h = row % p.heads, pos = (row / p.heads) % p.q_len, b = row / (p.heads * p.q_len);
   const int brow = p.rows != nullptr ? p.rows[b] : b;
   const int group = pos / kpos, r = (pos % kpos) * kHeadsMax + h;
@@ -1042,6 +1044,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) mla_merge_kernel(const MlaPa
   asm volatile("griddepcontrol.wait;" ::: "memory");  // the decode grid has completed and its partials are visible
   auto live = [](float2 v) { return v.y > 0.f || v.y != v.y; };  // a part without tokens has denominator 0
   float m_all = -INFINITY;
+#pragma unroll 8
   for (int q = lane; q < p.parts; q += 32) {
     const float2 v = ml[(slot0 + q) * R + r];
     if (live(v)) m_all = fmaxf(m_all, v.x);
@@ -1050,24 +1053,23 @@ __global__ void __launch_bounds__(kMergeWarps * 32) mla_merge_kernel(const MlaPa
   for (int o = 16; o > 0; o >>= 1) m_all = fmaxf(m_all, __shfl_xor_sync(0xffffffffu, m_all, o));
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   float l_all = 0.f;
-#pragma unroll 4
-  for (int q = warp; q < p.parts; q += kMergeWarps) {
+#pragma unroll 5
+  for (int q = warp; q < p.parts; q += nwarps) {
     const float2 v = ml[(slot0 + q) * R + r];
     const bool on = live(v);
     const float wgt = on ? ex2_approx(v.x - m_all) : 0.f;
-    float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (on) o = *reinterpret_cast<const float4*>(p.part_o + ((slot0 + q) * R + r) * kLat + quarter * 128 + lane * 4);
+    // (the outputs of a part without tokens were never written: read all the same, so that no load waits for another)
+    const float4 o = *reinterpret_cast<const float4*>(p.part_o + ((slot0 + q) * R + r) * kLat + quarter * 128 + lane * 4);
     l_all += wgt * v.y;
-    acc.x += wgt * o.x, acc.y += wgt * o.y, acc.z += wgt * o.z, acc.w += wgt * o.w;
+    if (on) acc.x += wgt * o.x, acc.y += wgt * o.y, acc.z += wgt * o.z, acc.w += wgt * o.w;
   }
-  __shared__ float4 acc_s[kMergeWarps][32];
-  __shared__ float l_s[kMergeWarps];
+  __shared__ float4 acc_s[kMergeWarpsMany][32];
+  __shared__ float l_s[kMergeWarpsMany];
   acc_s[warp][lane] = acc;
   if (lane == 0) l_s[warp] = l_all;
   __syncthreads();
   if (warp != 0) return;
-#pragma unroll
-  for (int k = 1; k < kMergeWarps; ++k) {
+  for (int k = 1; k < nwarps; ++k) {
     const float4 x = acc_s[k][lane];
     acc.x += x.x, acc.y += x.y, acc.z += x.z, acc.w += x.w;
     l_all += l_s[k];
@@ -1182,7 +1184,8 @@ cudaError_t launch_one(const MlaParams& params, cudaStream_t stream) {
   // run (they are small enough to sit beside a decode CTA) and wait there for the decode grid to complete.
   const bool few = p.parts <= kMergeFewParts;
   cudaLaunchConfig_t mcfg = {};
-  mcfg.gridDim = dim3(p.batch * p.q_len * p.heads * (few ? 1 : 4)), mcfg.blockDim = dim3(few ? 128 : kMergeWarps * 32);
+  mcfg.gridDim = dim3(p.batch * p.q_len * p.heads * (few ? 1 : 4));
+  mcfg.blockDim = dim3(few ? 128 : (p.parts > 64 ? kMergeWarpsMany : kMergeWarps) * 32);
   mcfg.stream = stream;
   cudaLaunchAttribute mattr[1];
   mattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
