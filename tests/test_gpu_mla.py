@@ -434,6 +434,65 @@ def test_paged_call_replays_from_a_cuda_graph(ma, cuda_device):
     _check(ma, o_lat, _oracle(q_lat, q_pe, kv, lens1), "graph replay, second lengths")
 
 
+@pytest.mark.parametrize("parts", [1, 4, 12])
+def test_calls_in_a_row_see_what_the_kernels_before_them_wrote(ma, cuda_device, parts):
+    """The decode kernel is launched as a programmatic dependent of its predecessor in the stream and sets up while
+    that one still runs; it must not read queries, cache rows or lengths before the predecessor has completed, and
+    what follows it must see its output.  Twelve steps without any synchronisation: a torch kernel writes new
+    queries, another appends a token row to the cache and a third bumps the lengths, the decode call runs, a
+    torch kernel copies the output away.  Every step's copy is checked at the end.  (1 part: the kernel writes the
+    output itself; 4: merge inside a cluster; 12: merge kernel.)"""
+    B, H, S0, steps = 3, 16, 600, 12
+    g = torch.Generator().manual_seed(5)
+    kv_all = torch.randn(B, S0 + steps, FUSED, generator=g).to(torch.float8_e4m3fnuz).to(cuda_device)
+    qs = [_rand_q(B, None, H, cuda_device, 100 + i)[:2] for i in range(steps)]
+    total = B * (S0 + steps)
+    pool = torch.zeros(total, 1, FUSED, dtype=torch.uint8, device=cuda_device)
+    slots = torch.arange(total, dtype=torch.int32, device=cuda_device)                      # request b owns rows b*(S0+steps)...
+    indptr = torch.arange(0, total + 1, S0 + steps, dtype=torch.int32, device=cuda_device)
+    pool.view(B, S0 + steps, FUSED)[:, :S0] = kv_all.view(torch.uint8)[:, :S0]
+    lens = torch.full((B,), S0, dtype=torch.int32, device=cuda_device)
+    q_lat, q_pe = qs[0][0].clone(), qs[0][1].clone()
+    o_lat = torch.zeros_like(q_lat)
+    outs = []
+    torch.cuda.synchronize()
+    for i in range(steps):
+        q_lat.copy_(qs[i][0])
+        q_pe.copy_(qs[i][1])
+        pool.view(B, S0 + steps, FUSED)[:, S0 + i] = kv_all.view(torch.uint8)[:, S0 + i]    # this step's new token
+        lens.add_(1)
+        ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool.view(torch.float8_e4m3fnuz), o_lat, lens, None, slots, indptr,
+                                      parts, SCALE, KV_SCALE)
+        outs.append(o_lat.clone())
+    torch.cuda.synchronize()
+    assert ma.last_status()[0] == 0
+    for i in range(steps):
+        ref = _oracle(qs[i][0], qs[i][1], kv_all, [S0 + i + 1] * B)
+        got = outs[i].float().cpu().numpy().reshape(ref.shape)
+        assert mo.rel_l2(got, ref) < REL_L2, f"step {i}: rel-L2 {mo.rel_l2(got, ref):.2e}"
+
+
+def test_status_word_is_cleared_by_the_call_itself(ma, cuda_device):
+    """No memset precedes the kernel: a workspace full of stale bytes (a status word left by a failed call
+    included) must not disturb the call, and its first status word must read zero afterwards."""
+    from moonmath_attention import _abi
+
+    B, H, S = 5, 16, 1000
+    kv = _rand_kv(B, S, cuda_device, 71)
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 71)
+    ref = _oracle(q_lat, q_pe, kv, [S] * B)
+    stream = torch.cuda.current_stream().cuda_stream
+    for parts in (1, 3, 20):
+        ws = torch.full((int(_abi.lib.ma_mla_workspace_bytes(B, 1, parts)),), 0xAB, dtype=torch.uint8, device=cuda_device)
+        o_lat.zero_()
+        rc = _abi.lib.ma_mla_decode_a16w8(q_lat.data_ptr(), q_pe.data_ptr(), kv.data_ptr(), o_lat.data_ptr(), None, None,
+                                          None, None, B, H, 1, S, parts, SCALE, KV_SCALE, 0, ws.data_ptr(), ws.numel(), stream)
+        assert rc == 0, _abi.error_string(rc)
+        torch.cuda.synchronize()
+        assert ws[:4].view(torch.int32).item() == 0
+        assert mo.rel_l2(o_lat.float().cpu().numpy().reshape(ref.shape), ref) < REL_L2, parts
+
+
 def test_contiguous_argument_errors(ma, cuda_device):
     kv = _rand_kv(2, 256, cuda_device, 83)
     q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
