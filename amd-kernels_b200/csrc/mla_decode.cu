@@ -161,7 +161,8 @@ struct Work {
   int q_len, heads;
   int pos0, npos;       // draft positions of this CTA
   int len;              // cached tokens of the request
-  int tile0, tiles;     // tiles [tile0, tile0 + tiles) of 128 tokens
+  int tile0, tiles;     // tiles [tile0, tile0 + tiles) of 96 tokens
+  int idx0;             // paged pool: where the request's slot numbers begin in kv_indices
   int end_max;          // tokens the last position of the group may see
 };
 
@@ -177,6 +178,8 @@ __device__ __forceinline__ Work decode_work(const MlaParams& p, int kpos) {
   w.heads = p.heads;
   w.pos0 = w.group * kpos;
   w.npos = min(kpos, p.q_len - w.pos0);
+  // (the three loads are independent of one another: one trip to memory, not three)
+  w.idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
   w.len = p.seq_lens != nullptr ? p.seq_lens[w.b] : p.seq;
   w.end_max = w.len - p.q_len + w.pos0 + w.npos;  // last position of the group, inclusive limit + 1
   const int total = w.end_max > 0 ? (w.end_max + kTok - 1) / kTok : 0;
@@ -225,7 +228,7 @@ __device__ __forceinline__ void role_copy(const MlaParams& p, const Work& w, uin
   // 16 bytes each.  Lane k < 12 holds the pool slot of the warp's k-th row, fetched one tile ahead, so that no
   // copy waits for an index load of its own.
   const uint8_t* kv = static_cast<const uint8_t*>(p.kv);
-  const int idx0 = p.kv_indptr != nullptr ? p.kv_indptr[w.b] : 0;
+  const int idx0 = w.idx0;
   const int warp = lt >> 5, lane = lt & 31;
   constexpr int kRowsPerWarp = kTok / (kCopyThreads / 32);  // 12 (eight warps) or 16 (six)
   constexpr int kPiecesPerWarp = kRowsPerWarp * 36;         // 432 = 13.5 warp-wide copies, or 576 = 18
