@@ -86,6 +86,14 @@ def test_no_gpu_means_an_error_not_a_fallback():
         ma.forward(q, q, q)
 
 
+def test_mla_cluster_capacity_domain():
+    """Outside 2..8 parts or q_len 1..8 there is no cluster; without a GPU the answer is 0 as well (a query, not a launch)."""
+    cap = _abi.lib.ma_mla_cluster_capacity
+    assert cap(1, 0, 1) == 0 and cap(1, 0, 9) == 0 and cap(0, 0, 4) == 0 and cap(9, 1, 4) == 0
+    if not torch.cuda.is_available():
+        assert cap(1, 0, 4) == 0 and cap(4, 1, 2) == 0
+
+
 def test_round_bf16_rejects_bad_arguments():
     assert _abi.lib.ma_round_bf16(0, 0, 0, 5, 0) == 8
     assert _abi.lib.ma_round_bf16(0, 0, 4, 0, 0) == 9
