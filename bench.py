@@ -253,7 +253,7 @@ def run_reference(args, rank: int, world: int) -> None:
 # ---------------------------------------------------------------------------------------------------
 MLA_SHAPE = {"batch": 148, "seq": 4096, "heads": 16}
 # dram__bytes_read.sum + dram__bytes_write.sum of one mla_decode_kernel launch at that shape (one ncu capture)
-MLA_NCU_TRAFFIC_BYTES = 352064000 + 3900416
+MLA_NCU_TRAFFIC_BYTES = 352065792 + 4044544
 
 
 def mla_cpu_oracle_rate(budget_s: float) -> dict:
@@ -302,6 +302,39 @@ def mla_device_record(ma, dev, seed: int, steps: int, world: int, peaks: dict) -
                         "peak_source": f"{peaks['source']} hbm_gbs"},
            "device_status": status[:3]}
     return rec, (step, q_lat, q_pe, o_lat, traffic)
+
+
+def mla_other_shapes(ma, dev, seed: int, peaks: dict) -> list:
+    """The decode step at mid batch (the parts of a request merged inside a thread-block cluster), for one long request
+    (merge kernel) and from a paged pool with one token per slot in random order; same timing as the main shape."""
+    out = []
+    H, scale, kv_scale = MLA_SHAPE["heads"], 576 ** -0.5, 1.0 / 32.0
+    for B, S, paged in ((64, 8192, False), (32, 8192, False), (1, 131072, False), (148, 4096, True)):
+        g = torch.Generator(device=dev)
+        g.manual_seed(seed + B)
+        kv = torch.randn(B, S, 576, generator=g, device=dev).to(torch.float8_e4m3fnuz)
+        q_lat = (torch.randn(B, H, 512, generator=g, device=dev) * 3).bfloat16()
+        q_pe = (torch.randn(B, H, 64, generator=g, device=dev) * 3).bfloat16()
+        o_lat = torch.zeros_like(q_lat)
+        if paged:
+            slots = torch.randperm(B * S, generator=g, device=dev).to(torch.int32)
+            pool = torch.empty(B * S, 1, 576, dtype=torch.uint8, device=dev)
+            pool[slots.long(), 0] = kv.view(torch.uint8).view(B * S, 576)
+            pool = pool.view(torch.float8_e4m3fnuz)
+            lens = torch.full((B,), S, dtype=torch.int32, device=dev)
+            indptr = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=dev)
+            parts = ma.mla_decode_a16w8_plan_parts_q(B, S, 1, H)
+            step = lambda: ma.mla_decode_a16w8_paged_dev(q_lat, q_pe, pool, o_lat, lens, None, slots, indptr, parts, scale, kv_scale)  # noqa: E731
+            del kv
+        else:
+            step = lambda: ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, scale, kv_scale)  # noqa: E731
+        for _ in range(5):
+            step()
+        ms = timed(step, 50, 1)
+        gbs = B * S * 576 / ms / 1e6
+        out.append({"batch": B, "seq": S, "cache": "paged pool, random slots" if paged else "contiguous slab", "us_per_call": ms * 1e3,
+                    "gb_per_s": gbs, "frac_of_hbm_peak": gbs / peaks["hbm"], "device_status": ma.last_status()[:1]})
+    return out
 
 
 def run_mla(args) -> None:
@@ -643,6 +676,7 @@ def main() -> None:
         line["parity"] = parity_record(ma, dev)
         line["lite"] = lite_record(ma, dev, peaks)
         line["mla"] = mla_device_record(ma, dev, 42 * 1000003, 50, 1, peaks)[0]
+        line["mla"]["other_shapes"] = mla_other_shapes(ma, dev, 42 * 1000003, peaks)
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_oracle_rate(Skv, B * H * Sq, 12.0, torch.get_num_threads())
     print(json.dumps(line), flush=True)
