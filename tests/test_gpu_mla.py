@@ -493,6 +493,21 @@ def test_status_word_is_cleared_by_the_call_itself(ma, cuda_device):
         assert mo.rel_l2(o_lat.float().cpu().numpy().reshape(ref.shape), ref) < REL_L2, parts
 
 
+def test_more_requests_than_sms_run_in_several_waves(ma, cuda_device):
+    """600 requests are four waves of CTAs; twice in a row, so that the second call's first wave lines up behind
+    the first call's last one (dependent launch) and must still wait for all of it."""
+    B, H, S = 600, 4, 200
+    kv = _rand_kv(B, S, cuda_device, 83)
+    q_lat, q_pe, o_lat = _rand_q(B, None, H, cuda_device, 83)
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    first = o_lat.clone()
+    o_lat.zero_()
+    ma.mla_decode_a16w8(q_lat, q_pe, kv, o_lat, SCALE, KV_SCALE)
+    ref = _oracle(q_lat, q_pe, kv, [S] * B)
+    _check(ma, o_lat, ref, "600 requests")
+    assert torch.equal(first.view(torch.int16), o_lat.view(torch.int16))
+
+
 def test_contiguous_argument_errors(ma, cuda_device):
     kv = _rand_kv(2, 256, cuda_device, 83)
     q_lat, q_pe, o_lat = _rand_q(2, None, 16, cuda_device, 83)
