@@ -389,7 +389,7 @@ int mla_plan(int batch, int q_len, int max_seq_len, int num_sms) {
   const int sms = resolve_sms(num_sms);
   if (sms <= 0) return 1;
   const int base = batch * mla_groups(q_len, mla_pos_per_cta(q_len));  // CTAs before any split
-  const int tiles = (max_seq_len + 127) / 128;            // 128-token tiles of the longest request
+  const int tiles = (max_seq_len + 127) / 128;            // planning unit: 128 tokens of the longest request
   int parts = sms / base;                                 // fill the GPU once ...
   const int by_length = (tiles + 3) / 4;                  // ... with at least four tiles (512 tokens) per part
   if (parts > by_length) parts = by_length;

@@ -189,7 +189,7 @@ __device__ __forceinline__ Work decode_work(const MlaParams& p, int kpos) {
   return w;
 }
 
-// ---------------------------------------------------------------------------
+// loaders.  Pools: eight (six) "copy" warps stream a tile of 96 token rows into the swizzled chunks with 16-byte
 // loaders.  Eight "copy" warps stream a tile of 128 token rows into the swizzled chunks with 16-byte
 // asynchronous copies (no registers in between) and hand completion to an mbarrier, so they never wait for
 // data and the next tile's copies start the moment its stage is free.  The MMA thread takes the landed tile
